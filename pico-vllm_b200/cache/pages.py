@@ -1,0 +1,62 @@
+"""A pool of numbered cache pages with reference counts.
+
+Pages are handed out from a free list and come back when their count falls to zero, so they are
+used again.  Counterpart of the reference's BlockManager bookkeeping (free deque, per-block
+reference count, free at zero: pico_vllm/blockmanager.py:63, 70-133), without its logical ->
+physical indirection and CPU tier.  Freeing a page that is not held raises instead of
+corrupting the list.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Iterable, List
+
+from ..errors import OutOfPages, PicoError
+
+
+class PagePool:
+    def __init__(self, num_pages: int):
+        if num_pages < 1:
+            raise PicoError("a page pool needs at least one page")
+        self.num_pages = num_pages
+        self._free = deque(range(num_pages))
+        self._refs = [0] * num_pages
+
+    @property
+    def available(self) -> int:
+        return len(self._free)
+
+    @property
+    def in_use(self) -> int:
+        return self.num_pages - len(self._free)
+
+    def allocate(self, n: int) -> List[int]:
+        """n pages, each with count 1; all or nothing."""
+        if n > len(self._free):
+            raise OutOfPages(f"{n} pages wanted, {len(self._free)} of {self.num_pages} free")
+        pages = [self._free.popleft() for _ in range(n)]
+        for p in pages:
+            self._refs[p] = 1
+        return pages
+
+    def share(self, pages: Iterable[int]) -> None:
+        """One more holder for each page (pico_vllm/blockmanager.py:120-124)."""
+        for p in pages:
+            if self._refs[p] < 1:
+                raise PicoError(f"page {p} is not held, it cannot be shared")
+            self._refs[p] += 1
+
+    def release(self, pages: Iterable[int]) -> List[int]:
+        """One holder fewer for each page; returns the pages that became free."""
+        freed = []
+        for p in pages:
+            if not 0 <= p < self.num_pages or self._refs[p] < 1:
+                raise PicoError(f"page {p} is released but not held")
+            self._refs[p] -= 1
+            if self._refs[p] == 0:
+                self._free.append(p)
+                freed.append(p)
+        return freed
+
+    def refcount(self, page: int) -> int:
+        return self._refs[page]

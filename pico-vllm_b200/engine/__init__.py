@@ -1,0 +1,6 @@
+from .batch import Batch, GroupBatch
+from .runner import ModelRunner, StepItem
+from .core import load_model, model_from_tensors, make_cache, make_runner
+
+__all__ = ["Batch", "GroupBatch", "ModelRunner", "StepItem", "load_model", "model_from_tensors",
+           "make_cache", "make_runner"]

@@ -1,0 +1,295 @@
+"""The step function: runs a batch of (request, its next tokens) through the model, from the
+cache, and returns logits at the wanted places.
+
+``ModelRunner.step(items)`` takes pages for the new tokens, builds the index arrays on the host
+(one packed int32 buffer, one host-to-device copy), calls the model once for the whole batch
+and commits the tokens to the cache.  Portions of prompts and single decoded tokens share the
+batch; nothing but the given tokens is computed.  Steps that hold only single tokens are
+replayed from a CUDA graph per batch-size bucket (the reference captures one graph at a fixed
+batch of 8 and pads with ghost rows, pico_vllm/engine.py:98-191); padding rows have position
+-1, which every kernel treats as "no keys, no store".
+
+Counterpart of the tensor building in pico_vllm/engine.py:146-181, 199-220, 325-342, which
+runs one forward per prompt plus one for all decoding requests.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager
+from ..config.engine import EngineConfig
+from ..errors import PicoError, ScheduleError
+from .batch import Batch, GroupBatch
+
+
+@dataclass
+class StepItem:
+    slot: int                    # the request's cache slot
+    tokens: Sequence[int]        # its next tokens (one or more)
+    want: Sequence[int] = ()     # places among these tokens whose logits are asked for
+
+
+class _Layout:
+    """Offsets of the index arrays inside one packed int32 buffer."""
+
+    def __init__(self, T: int, S: int, R: int, n_groups: int, width: int):
+        self.T, self.S, self.R, self.width = T, S, R, width
+        off = 0
+
+        def take(n):
+            nonlocal off
+            start = off
+            off += (n + 3) // 4 * 4     # keep every array 16-byte aligned
+            return start
+        self.token_ids, self.positions, self.tok_seg = take(T), take(T), take(T)
+        self.seg_slots, self.cu_q, self.logit_rows = take(S), take(S + 1), take(R)
+        self.g_slots = [take(T) for _ in range(n_groups)]
+        self.g_tables = [take(S * width) for _ in range(n_groups)]
+        self.total = off
+
+
+class _Staging:
+    """A pinned host buffer, its device twin and an event that tells when the last copy is done
+    (the host buffer is not rewritten before that)."""
+
+    def __init__(self, n: int, device: torch.device):
+        cuda = device.type == "cuda"
+        self.host = torch.empty(n, dtype=torch.int32, pin_memory=cuda)
+        self.dev = torch.empty(n, dtype=torch.int32, device=device)
+        self.event = torch.cuda.Event() if cuda else None
+        self.busy = False
+
+    def wait(self):
+        if self.event is not None and self.busy:
+            self.event.synchronize()
+            self.busy = False
+
+    def upload(self, n: int):
+        self.dev[:n].copy_(self.host[:n], non_blocking=True)
+        if self.event is not None:
+            self.event.record()
+            self.busy = True
+
+
+class ModelRunner:
+    def __init__(self, model, cache: CacheManager, cfg: EngineConfig):
+        self.model, self.cache, self.cfg = model, cache, cfg
+        self.device = cache.device
+        self.on_gpu = self.device.type == "cuda"
+        self.views = cache.views()
+        self._graphs: Dict[int, dict] = {}
+        self._scratch: Optional[torch.Tensor] = None
+        self._stage: Optional[_Staging] = None
+        self.graph_replays = 0
+        self.steps = 0
+        kv = [g.spec for g in cache.groups]
+        self._max_heads = 0
+        for blk in model.blocks:
+            m = blk.mixer
+            if hasattr(m, "n_heads"):
+                self._max_heads = max(self._max_heads, m.n_heads * (m.head_dim + 2))
+        self._min_kv_heads = min((s.n_kv_heads for s in kv), default=1)
+
+    # ------------------------------------------------------------------ buffers
+    def _staging(self, n: int) -> _Staging:
+        if self._stage is None or self._stage.host.numel() < n:
+            if self._stage is not None:
+                self._stage.wait()
+            self._stage = _Staging(max(n, 4096), self.device)
+        return self._stage
+
+    def _splits(self, T: int, max_kv: int) -> int:
+        """How many parts to cut each token's key range into: enough blocks to fill the GPU
+        when the batch is small and the context long."""
+        blocks = max(1, T * self._min_kv_heads)
+        want = -(-592 // blocks)                      # ~4 blocks per SM on 148 SMs
+        most = max(1, max_kv // 128)
+        return int(max(1, min(want, most, 64)))
+
+    def _scratch_for(self, T: int, splits: int) -> Optional[torch.Tensor]:
+        if splits <= 1:
+            return None
+        need = T * splits * self._max_heads
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+        return self._scratch
+
+    # ------------------------------------------------------------------ the step
+    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+        """Runs the items as one batch; returns float32 logits [wanted, vocab] on the device, in
+        the order of the items and of each item's ``want``.  The result of a graph-replayed step
+        lives in a buffer that the next such step overwrites."""
+        if not items:
+            return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
+        V = self.model.vocab_size
+        seen = set()
+        for it in items:
+            if len(it.tokens) < 1:
+                raise PicoError("a step item needs at least one token")
+            if it.slot in seen:
+                raise PicoError(f"slot {it.slot} appears twice in one step")
+            seen.add(it.slot)
+            if min(it.tokens) < 0 or max(it.tokens) >= V:
+                raise PicoError(f"token id outside [0, {V}) in a step item")
+            for w in it.want:
+                if not 0 <= w < len(it.tokens):
+                    raise PicoError(f"wanted place {w} outside the {len(it.tokens)} tokens given")
+        starts = []
+        done = []
+        try:
+            for it in items:
+                starts.append(self.cache.append(it.slot, len(it.tokens)))
+                done.append(it.slot)
+        except Exception:
+            for s in done:
+                self.cache.rollback(s)
+            raise
+        decode_only = all(len(it.tokens) == 1 for it in items)
+        try:
+            if (decode_only and self.cfg.use_cuda_graph and self.on_gpu
+                    and len(items) <= max(self.cfg.graph_batch_sizes)):
+                logits = self._step_graph(items, starts)
+            else:
+                batch = self._build(items, starts, pad_to=None)
+                logits = self.model.forward(batch, self.views)
+        except Exception:
+            for it in items:
+                self.cache.rollback(it.slot)
+            raise
+        for it in items:
+            self.cache.commit(it.slot)
+        self.steps += 1
+        return logits
+
+    def _build(self, items: Sequence[StepItem], starts: List[int], pad_to: Optional[int],
+               splits: Optional[int] = None, buffers=None, scratch=None) -> Batch:
+        """Index arrays of the step on the device.  ``pad_to``: number of one-token segments of
+        a graph bucket (the batch is padded to it and the block tables keep their full width);
+        ``buffers``/``scratch``: the bucket's own staging and scratch tensors, which must not move."""
+        cache = self.cache
+        S_real = len(items)
+        q_lens = [len(it.tokens) for it in items]
+        T_real = sum(q_lens)
+        S = pad_to or S_real
+        T = T_real + (S - S_real)
+        want_rows: List[int] = []
+        at = 0
+        for it, n in zip(items, q_lens):
+            want_rows.extend(at + w for w in it.want)
+            at += n
+        R_real = len(want_rows)
+        R = R_real if pad_to is None else S     # a graph's shape is fixed: one row per segment
+        if pad_to is not None and R_real > R:
+            raise PicoError("more logits wanted than the graph holds")
+        kv_lens = [st + n for st, n in zip(starts, q_lens)]
+        if pad_to is None:
+            W = min(cache.max_blocks, (-(-max(kv_lens) // cache.page_size) + 3) // 4 * 4)
+        else:
+            W = cache.max_blocks
+        lay = _Layout(T, S, R, len(cache.groups), W)
+        stage = buffers if buffers is not None else self._staging(lay.total)
+        stage.wait()
+        dev = stage.dev
+        h = stage.host.numpy()
+        tok = h[lay.token_ids:lay.token_ids + T]
+        pos = h[lay.positions:lay.positions + T]
+        seg = h[lay.tok_seg:lay.tok_seg + T]
+        tok[:] = 0
+        pos[:] = -1
+        seg[:] = 0
+        cu = h[lay.cu_q:lay.cu_q + S + 1]
+        ss = h[lay.seg_slots:lay.seg_slots + S]
+        ss[:] = 0
+        at = 0
+        for i, (it, n, st) in enumerate(zip(items, q_lens, starts)):
+            tok[at:at + n] = np.asarray(it.tokens, dtype=np.int32)
+            pos[at:at + n] = np.arange(st, st + n, dtype=np.int32)
+            seg[at:at + n] = i
+            cu[i] = at
+            ss[i] = it.slot
+            at += n
+        for i in range(S_real, S):      # padding segments of one token each
+            seg[at] = i
+            cu[i] = at
+            at += 1
+        cu[S] = at
+        rows = h[lay.logit_rows:lay.logit_rows + R]
+        rows[:] = 0
+        rows[:R_real] = np.asarray(want_rows, dtype=np.int32)
+        for gi, g in enumerate(cache.groups):
+            sl = h[lay.g_slots[gi]:lay.g_slots[gi] + T]
+            sl[:] = -1
+            tb = h[lay.g_tables[gi]:lay.g_tables[gi] + S * W].reshape(S, W)
+            tb[:] = 0
+            at = 0
+            for i, (it, n, st) in enumerate(zip(items, q_lens, starts)):
+                sl[at:at + n] = cache.slot_mapping(gi, it.slot, st, n)
+                row = cache.table_row(gi, it.slot)
+                tb[i] = np.maximum(row[:W], 0)  # blocks without a page are never read; keep indices legal
+                at += n
+        stage.upload(lay.total)
+
+        def d(off, n):
+            return dev[off:off + n]
+        groups = {gi: GroupBatch(d(lay.g_slots[gi], T), d(lay.g_tables[gi], S * W).view(S, W))
+                  for gi in range(len(cache.groups))}
+        max_kv = max(kv_lens)
+        if splits is None:
+            splits = self._splits(T, max_kv)
+        return Batch(num_tokens=T, num_segments=S, token_ids=d(lay.token_ids, T), positions=d(lay.positions, T),
+                     tok_seg=d(lay.tok_seg, T), seg_slots=d(lay.seg_slots, S), cu_q=d(lay.cu_q, S + 1),
+                     logit_rows=d(lay.logit_rows, R), num_logit_rows=R, groups=groups, q_lens=q_lens,
+                     kv_lens=kv_lens, attn_splits=splits,
+                     scratch=scratch if scratch is not None else self._scratch_for(T, splits),
+                     decode_only=all(n == 1 for n in q_lens))
+
+    # ------------------------------------------------------------------ CUDA graph replay of decode steps
+    def _bucket(self, n: int) -> int:
+        return min(b for b in self.cfg.graph_batch_sizes if b >= n)
+
+    def _step_graph(self, items: Sequence[StepItem], starts: List[int]) -> torch.Tensor:
+        B = self._bucket(len(items))
+        # every segment has one token; logits are computed for every row of the bucket
+        full = [StepItem(it.slot, it.tokens, (0,)) for it in items]
+        entry = self._graphs.get(B)
+        if entry is None:
+            entry = self._capture(B, full, starts)
+        else:
+            self._build(full, starts, pad_to=B, splits=entry["splits"], buffers=entry["buffers"],
+                        scratch=entry["scratch"])
+            entry["graph"].replay()
+            ops._count(entry["launches"])
+        self.graph_replays += 1
+        logits = entry["logits"]
+        rows = [i for i, it in enumerate(items) if len(it.want)]
+        if len(rows) == len(items):
+            return logits[:len(items)]
+        return logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else logits[:0]
+
+    def _capture(self, B: int, items: Sequence[StepItem], starts: List[int]) -> dict:
+        """First decode step at this bucket: run it once eagerly (this also warms up the
+        libraries), then record the same work into a graph over the same buffers."""
+        # a graph keeps the addresses it was recorded with: the bucket owns its staging and scratch
+        lay = _Layout(B, B, B, len(self.cache.groups), self.cache.max_blocks)
+        buffers = _Staging(lay.total, self.device)
+        splits = self._splits(B, min(self.cache.max_seq_len, 4096))
+        scratch = (torch.empty(B * splits * self._max_heads, dtype=torch.float32, device=self.device)
+                   if splits > 1 else None)
+        batch = self._build(items, starts, pad_to=B, splits=splits, buffers=buffers, scratch=scratch)
+        self.model.forward(batch, self.views)           # eager warm-up; writes the same cache rows
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.views)
+        launches = ops.launches - before
+        graph.replay()
+        entry = {"graph": graph, "logits": logits, "splits": splits, "launches": launches, "batch": batch,
+                 "buffers": buffers, "scratch": scratch}
+        self._graphs[B] = entry
+        return entry

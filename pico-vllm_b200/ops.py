@@ -1,0 +1,280 @@
+"""Python face of the CUDA kernels: one function per kernel family.
+
+Each function checks shapes, dtypes and devices on the host, refuses sizes the kernels do not
+take with a :class:`KernelError`, and launches on torch's current CUDA stream.  The library is
+loaded (and, if needed, compiled) at the first call.  There is no CPU path: tensors on another
+device are refused.
+
+Matrix products go to the library (``torch.mm``, cuBLAS), as in the reference, whose
+projections are ``nn.Linear`` (pico_vllm/model.py:147-152, 309-312); everything else on the
+forward path is a kernel of ``csrc/``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .errors import KernelError
+
+_F32, _BF16 = 0, 1
+_lib = None
+launches = 0  # kernels of this package launched so far (graph replays add their captured count)
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def library():
+    """The loaded kernel library (ctypes); loads and builds it at first use."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this engine runs on a GPU only (there is no CPU path)")
+    from .csrc import library_path
+    path = library_path()
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as e:
+        raise KernelError(f"cannot load the kernel library {path}: {e}") from None
+    vp, i32, f32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+    sigs = {
+        "pico_embedding": [vp, vp, i32, vp, i32, i32, i32, vp],
+        "pico_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
+        "pico_swiglu": [vp, vp, i32, i32, i32, vp],
+        "pico_rope_store": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
+        "pico_paged_attention_generic": [vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
+                                         i32, i32, f32, i32, i32, vp],
+        "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
+        "pico_bf16_to_f32": [vp, vp, i64, vp],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    reasons = {-2: "an element type the kernel does not take", -3: "a size the kernel does not take",
+               -4: "a misaligned row stride"}
+    if code in reasons:
+        raise KernelError(f"{what}: {reasons[code]}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must be CUDA tensors (there is no CPU path)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _count(n: int = 1) -> None:
+    global launches
+    launches += n
+
+
+# ------------------------------------------------------------------------------------------
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = float32(table[ids[t], :]).  ids int32 [T]; table [V, H]; out float32 [T, H]."""
+    _cuda(ids, table, out)
+    T, (V, H) = ids.shape[0], table.shape
+    if ids.dtype != torch.int32 or out.dtype != torch.float32 or out.shape != (T, H):
+        raise KernelError("embedding: ids must be int32 [T] and out float32 [T, H]")
+    if not (table.is_contiguous() and out.is_contiguous() and ids.is_contiguous()):
+        raise KernelError("embedding: tensors must be contiguous")
+    _check(library().pico_embedding(_ptr(ids), _ptr(table), _dtype_code(table), _ptr(out), T, H, V, _stream()),
+           "embedding")
+    _count()
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Residual add and RMS norm in one pass.
+
+    x float32 [T, H] is the residual stream.  Without ``rows``: x += delta (written back) and
+    out = norm(x) * weight for every row.  With ``rows`` (int32 [R]): out[r] = norm(x[rows[r]] +
+    delta[rows[r]]) * weight and x is not changed.  delta may be None.  weight float32 [H].
+    """
+    _cuda(x, delta, weight, out, rows)
+    H = x.shape[1]
+    R = rows.shape[0] if rows is not None else x.shape[0]
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or weight.shape != (H,):
+        raise KernelError("add_rmsnorm: x must be float32 [T, H] and weight float32 [H]")
+    if out.shape != (R, H) or (delta is not None and (delta.shape != x.shape or delta.dtype != out.dtype)):
+        raise KernelError("add_rmsnorm: out must be [rows, H] and delta like x in out's dtype")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("add_rmsnorm: rows must be int32")
+    if not (x.is_contiguous() and out.is_contiguous() and (delta is None or delta.is_contiguous())):
+        raise KernelError("add_rmsnorm: tensors must be contiguous")
+    _check(library().pico_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), R, H,
+                                      float(eps), _dtype_code(out), _stream()), f"add_rmsnorm (width {H})")
+    _count()
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:], float32 inside."""
+    _cuda(gate_up, out)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: gate_up must be [T, 2*I] in out's dtype")
+    if not (gate_up.is_contiguous() and out.is_contiguous()):
+        raise KernelError("swiglu: tensors must be contiguous")
+    _check(library().pico_swiglu(_ptr(gate_up), _ptr(out), T, I, _dtype_code(out), _stream()), "swiglu")
+    _count()
+    return out
+
+
+def rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+               inv_freq: torch.Tensor, slots: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
+               v_pages: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int,
+               page_size: int) -> None:
+    """Adds the bias, rotates q (in place) and k, and stores k and v into their cache pages.
+
+    qkv [T, (n_heads + 2 n_kv_heads) head_dim]; bias float32 or None; positions, slots int32 [T]
+    (slot = page * page_size + offset, -1 = do not store); inv_freq float32 [rot_dim / 2];
+    pages [num_pages, n_kv_heads, page_size, head_dim] in qkv's dtype.  With slots None only q
+    is rotated.
+    """
+    _cuda(qkv, bias, positions, inv_freq, slots, k_pages, v_pages)
+    T = qkv.shape[0]
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    if qkv.shape[1] != width or qkv.stride(1) != 1:
+        raise KernelError(f"rope_store: qkv must have {width} contiguous columns")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (width,)):
+        raise KernelError("rope_store: bias must be float32 of the qkv width")
+    if positions.dtype != torch.int32 or inv_freq.dtype != torch.float32:
+        raise KernelError("rope_store: positions int32, inv_freq float32")
+    if slots is not None:
+        if slots.dtype != torch.int32 or k_pages is None or v_pages is None:
+            raise KernelError("rope_store: slots must be int32 and come with pages")
+        for p in (k_pages, v_pages):
+            if p.dtype != qkv.dtype or not p.is_contiguous() or tuple(p.shape[1:]) != (n_kv_heads, page_size, head_dim):
+                raise KernelError("rope_store: pages must be contiguous [pages, kv_heads, page_size, head_dim] in qkv's dtype")
+    _check(library().pico_rope_store(_ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(positions), _ptr(inv_freq),
+                                     _ptr(slots), _ptr(k_pages), _ptr(v_pages), T, n_heads, n_kv_heads,
+                                     head_dim, 2 * inv_freq.shape[0], page_size, _dtype_code(qkv), _stream()),
+           f"rope_store (head_dim {head_dim})")
+    _count()
+
+
+def attention_scratch_floats(T: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    """Float32 elements of scratch that paged_attention needs for n_splits > 1."""
+    return 0 if n_splits <= 1 else T * n_heads * n_splits * (head_dim + 2)
+
+
+def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                    tok_seg: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+                    n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
+                    scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of every token of the batch over its request's cache pages.
+
+    q: [T, >= n_heads*head_dim] rows (the qkv buffer, queries first); out [T, n_heads*head_dim];
+    tok_seg int32 [T]: row of block_table for each token; positions int32 [T]; block_table int32
+    [segments, width].  The token at position p sees keys max(0, p+1-window) .. p.  n_splits > 1
+    cuts each token's key range into parts that run in parallel and needs ``scratch`` (float32,
+    attention_scratch_floats elements).
+    """
+    _cuda(q, k_pages, v_pages, out, tok_seg, positions, block_table, scratch)
+    T = q.shape[0]
+    if head_dim % 16 != 0 or head_dim > 256:
+        raise KernelError(f"paged_attention: head_dim must be a multiple of 16 up to 256, got {head_dim}")
+    if n_heads % n_kv_heads != 0:
+        raise KernelError("paged_attention: n_heads must be a multiple of n_kv_heads")
+    if q.stride(1) != 1 or q.shape[1] < n_heads * head_dim or out.shape != (T, n_heads * head_dim):
+        raise KernelError("paged_attention: bad q or out shape")
+    if not (out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.stride(1) == 1):
+        raise KernelError("paged_attention: out, pages and block_table rows must be contiguous")
+    if tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError("paged_attention: pages must be [pages, kv_heads, page_size, head_dim]")
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
+        raise KernelError("paged_attention: q, pages and out must share one dtype")
+    for t in (tok_seg, positions, block_table):
+        if t.dtype != torch.int32:
+            raise KernelError("paged_attention: index tensors must be int32")
+    part_o = part_ml = None
+    if n_splits > 1:
+        need = attention_scratch_floats(T, n_heads, head_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"paged_attention: n_splits={n_splits} needs {need} float32 of scratch")
+        part_o = scratch.data_ptr()
+        part_ml = part_o + 4 * T * n_heads * n_splits * head_dim
+    _check(library().pico_paged_attention_generic(
+        _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o, part_ml, _ptr(tok_seg),
+        _ptr(positions), _ptr(block_table), block_table.stride(0), T, n_heads, n_kv_heads, head_dim, page_size,
+        int(window) if window else 0, float(scale), n_splits, _dtype_code(q), _stream()),
+        f"paged_attention (head_dim {head_dim})")
+    _count(2 if n_splits > 1 else 1)
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, K] times weight[N, K] transposed, a library matrix product (cuBLAS through torch).
+
+    A weight kept in float32 beside bfloat16 activations is multiplied in float32 and the result
+    rounded to bfloat16.  float32 products never use a reduced-precision (TF32) mode.
+    """
+    _cuda(x, weight)
+    if x.dtype == weight.dtype:
+        if out is None:
+            return torch.mm(x, weight.t())
+        return torch.mm(x, weight.t(), out=out)
+    if weight.dtype == torch.float32 and x.dtype == torch.bfloat16:
+        y = torch.mm(x.float(), weight.t()).to(torch.bfloat16)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    raise KernelError(f"linear: activations {x.dtype} with weights {weight.dtype} is not supported")
+
+
+def logits_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Float32 logits x [R, K] times weight[V, K] transposed (library matrix product)."""
+    _cuda(x, weight)
+    if x.dtype == torch.float32 and weight.dtype == torch.float32:
+        return torch.mm(x, weight.t())
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        return torch.mm(x, weight.t(), out_dtype=torch.float32)
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.float32:
+        return torch.mm(x.float(), weight.t())
+    raise KernelError(f"logits_linear: activations {x.dtype} with weights {weight.dtype} is not supported")
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
+           uniform: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """Chooses one token per row of float32 logits [R, V]: argmax where temperature is 0 (or
+    temperature is None), else inverse-CDF sampling of softmax(logits / temperature) restricted
+    to the top-p set, with the row's uniform number in [0, 1).  out int32 [R]."""
+    _cuda(logits, temperature, top_p, uniform, out)
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32 or out.shape != (R,):
+        raise KernelError("sample: logits float32 [R, V], out int32 [R]")
+    for t in (temperature, top_p, uniform):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (R,)):
+            raise KernelError("sample: temperature, top_p and uniform must be float32 [R]")
+    if temperature is not None and uniform is None:
+        raise KernelError("sample: sampling needs uniform numbers")
+    _check(library().pico_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_p),
+                                 _ptr(uniform), _ptr(out), _stream()), "sample")
+    _count()
+    return out

@@ -1,0 +1,56 @@
+"""Grouped-query attention over the paged cache: the mixer of this architecture.
+
+qkv projection (bias added inside the rotary kernel) -> rotation of q and k and store of k, v
+into pages (one kernel) -> paged causal attention (optionally over a window) -> output
+projection.  Same order as pico_vllm/model.py:200-227 (projection, split, RoPE, cache store,
+paged attention, o_proj); scale head_dim^-1/2 (pico_vllm/kernels/attention.py:92,231).  One
+code path serves portions of prompts and single decoded tokens; the reference has three
+(pico_vllm/model.py:186-302).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from .base import CacheView, PagedKV, Param, Part, Piece
+from .registry import register
+
+
+@register("mixer", "gqa_attention")
+class GQAAttention(Part):
+    def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position: Part,
+                 qkv_bias: bool = True, window: Optional[int] = None, scale: Optional[float] = None):
+        self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
+        self.position, self.has_bias, self.window = position, qkv_bias, window
+        self.scale = head_dim ** -0.5 if scale is None else scale
+        self.qkv_weight = self.qkv_bias = self.o_weight = None
+
+    def params(self) -> List[Param]:
+        q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        ps = [Param("qkv_weight", (Piece("q.weight", (q, self.width)), Piece("k.weight", (kv, self.width)),
+                                   Piece("v.weight", (kv, self.width)))),
+              Param("o_weight", (Piece("o.weight", (self.width, q)),))]
+        if self.has_bias:
+            ps.append(Param("qkv_bias", (Piece("q.bias", (q,)), Piece("k.bias", (kv,)), Piece("v.bias", (kv,))),
+                            kind="vector"))
+        return ps
+
+    def cache_spec(self):
+        return PagedKV(self.n_kv_heads, self.head_dim, self.window)
+
+    def materialize(self, device, dtype):
+        self.position.materialize(device, dtype)
+
+    def forward(self, h: torch.Tensor, batch, cache: CacheView) -> torch.Tensor:
+        gb = batch.groups[cache.group]
+        qkv = ops.linear(h, self.qkv_weight)
+        ops.rope_store(qkv, self.qkv_bias, batch.positions, self.position.inv_freq,
+                       gb.slots if cache.store else None, cache.k, cache.v,
+                       self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size)
+        out = torch.empty((h.shape[0], self.n_heads * self.head_dim), dtype=h.dtype, device=h.device)
+        ops.paged_attention(qkv, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
+                            self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size, self.window,
+                            self.scale, batch.attn_splits, batch.scratch)
+        return ops.linear(out, self.o_weight)

@@ -1,0 +1,93 @@
+"""What every part of a layer has in common.
+
+A *part* is one piece of a layer: a mixer (attention here), a feed-forward, a norm, a position
+encoding, the token embedding, the output head.  A part takes all of its sizes and constants as
+constructor arguments, declares the tensors it owns (:class:`Param`) and what cache it needs
+(:class:`PagedKV`, :class:`FixedState` or nothing), and never learns which model it is in: the
+model builder maps the part's local tensor keys to the tensor names of a model folder.
+
+Interfaces (duck-typed; subclassing :class:`Part` is enough):
+
+* Mixer: ``cache_spec()``, ``forward(h, batch, cache) -> delta`` with h [T, width] in the
+  activation dtype, ``batch`` a :class:`~pico_vllm_b200.engine.batch.Batch`, ``cache`` a
+  :class:`CacheView` of this call's cache entry.
+* Feed-forward: ``forward(h, batch) -> delta``.
+* Norm: ``add_norm(x, delta, rows=None) -> y`` on the float32 residual stream.
+* Position encoding: owned by the mixer that uses it; see ``parts/rotary.py``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class Piece:
+    """One tensor of the model folder that goes into a parameter."""
+    key: str                 # the part's own name for it, e.g. "q.weight"
+    shape: Tuple[int, ...]
+
+
+@dataclass(frozen=True)
+class Param:
+    """A tensor a part owns: its pieces are concatenated along dimension 0 at load time
+    (as the reference fuses q/k/v and gate/up, pico_vllm/weights.py:42-43,58)."""
+    attr: str
+    pieces: Tuple[Piece, ...]
+    kind: str = "matrix"     # "matrix": model dtype unless stored in 32-bit; "vector": float32
+    init: str = "normal"     # random-weights rule: "normal" N(0, std) or "one_plus_normal"
+
+    @property
+    def shape(self) -> Tuple[int, ...]:
+        first = self.pieces[0].shape
+        return (sum(p.shape[0] for p in self.pieces),) + tuple(first[1:])
+
+
+@dataclass(frozen=True)
+class PagedKV:
+    """The mixer keeps keys and values per token in pages.  ``window``: None = all keys stay
+    needed; W = only the last W keys are ever read, older pages may be given back."""
+    n_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class FixedState:
+    """The mixer keeps one tensor of fixed shape per request (zeroed when a request starts)."""
+    shape: Tuple[int, ...]
+    dtype: str = "float32"
+
+
+@dataclass
+class CacheView:
+    """What a mixer call gets of the cache: the tensors of its own cache entry.
+
+    For PagedKV: ``k`` and ``v`` are [num_pages, n_kv_heads, page_size, head_dim], ``group``
+    selects ``batch.groups[group]`` (slots and block table), ``store`` is False when this call
+    only reads an entry that another call fills.  For FixedState: ``state`` is
+    [max_num_seqs, *shape]; ``batch.seg_slots`` gives each segment's row."""
+    group: Optional[int] = None
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    page_size: int = 0
+    store: bool = True
+    state: Optional[torch.Tensor] = None
+
+
+class Part:
+    """Base of all parts: declares parameters, receives them from the loader."""
+
+    def params(self) -> List[Param]:
+        return []
+
+    def assign(self, attr: str, tensor: torch.Tensor) -> None:
+        setattr(self, attr, tensor)
+
+    def materialize(self, device: torch.device, dtype: torch.dtype) -> None:
+        """Creates device-side constants that are not weights (tables of frequencies …)."""
+
+    def cache_spec(self):
+        return None

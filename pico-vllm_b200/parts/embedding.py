@@ -1,0 +1,44 @@
+"""Token embedding and output head.
+
+x = E[ids] (pico_vllm/model.py:405,427) into the float32 residual stream; logits = y . W^T with
+W the embedding matrix when tied (pico_vllm/model.py:445) or a matrix of its own (the reference
+creates lm_head for the untied case but never uses it, pico_vllm/model.py:409-412; its older
+model does, pico_vllm/legacy/model.py:223-226).  Logits are float32 and are computed only for
+the rows that were asked for.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from .base import Param, Part, Piece
+
+
+class TokenEmbedding(Part):
+    def __init__(self, vocab: int, width: int):
+        self.vocab, self.width = vocab, width
+        self.weight = None
+
+    def params(self) -> List[Param]:
+        return [Param("weight", (Piece("weight", (self.vocab, self.width)),))]
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((ids.shape[0], self.width), dtype=torch.float32, device=ids.device)
+        return ops.embedding(ids, self.weight, out)
+
+
+class OutputHead(Part):
+    def __init__(self, vocab: int, width: int, tied_to: Optional[TokenEmbedding] = None):
+        self.vocab, self.width, self.tied_to = vocab, width, tied_to
+        self.weight = None
+
+    def params(self) -> List[Param]:
+        if self.tied_to is not None:
+            return []
+        return [Param("weight", (Piece("weight", (self.vocab, self.width)),))]
+
+    def forward(self, y: torch.Tensor) -> torch.Tensor:
+        w = self.tied_to.weight if self.tied_to is not None else self.weight
+        return ops.logits_linear(y, w)

@@ -1,0 +1,35 @@
+"""Gated feed-forward: down( act(gate(h)) * up(h) ) with gate and up as one matrix.
+
+pico_vllm/model.py:309-318 (fused gate_up projection, silu(gate) * up, down projection);
+the activation runs in float32 as in pico_vllm/kernels/swiglu.py:28-44.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import ops
+from ..errors import ConfigError
+from .base import Param, Part, Piece
+from .registry import register
+
+
+@register("feed_forward", "gated_mlp")
+class GatedMLP(Part):
+    def __init__(self, width: int, inner: int, act: str = "silu"):
+        if act != "silu":
+            raise ConfigError(f"gated_mlp: activation {act!r} is not built (only 'silu')")
+        self.width, self.inner = width, inner
+        self.gate_up_weight = self.down_weight = None
+
+    def params(self) -> List[Param]:
+        return [Param("gate_up_weight", (Piece("gate.weight", (self.inner, self.width)),
+                                         Piece("up.weight", (self.inner, self.width)))),
+                Param("down_weight", (Piece("down.weight", (self.width, self.inner)),))]
+
+    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
+        gu = ops.linear(h, self.gate_up_weight)
+        a = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+        ops.swiglu(gu, a)
+        return ops.linear(a, self.down_weight)

@@ -1,0 +1,135 @@
+"""Test doubles of the CUDA kernels in plain torch, for tests of host-side logic on the CPU.
+
+``install(monkeypatch)`` replaces the functions of ``pico_vllm_b200.ops`` so that the step
+function, the cache and the scheduler can be driven without a GPU.  These doubles also serve
+as the plain reference of each kernel in the GPU tests (same signatures, float32 arithmetic).
+They are not part of the product: the package itself has no CPU path.
+"""
+import math
+
+import torch
+
+import plain_qwen2 as plain
+
+
+def embedding(ids, table, out):
+    out.copy_(table[ids.long()].float())
+    return out
+
+
+def add_rmsnorm(x, delta, weight, eps, out, rows=None):
+    if rows is None:
+        if delta is not None:
+            x.add_(delta.float())
+        src = x
+    else:
+        src = x[rows.long()]
+        if delta is not None:
+            src = src + delta[rows.long()].float()
+    out.copy_(plain.rms_norm(src, weight, eps).to(out.dtype))
+    return out
+
+
+def swiglu(gate_up, out):
+    I = out.shape[1]
+    g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
+    out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
+    return out
+
+
+def rope_store(qkv, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads, head_dim,
+               page_size):
+    T = qkv.shape[0]
+    x = qkv.float()
+    if bias is not None:
+        x = x + bias
+    nq, nk = n_heads * head_dim, n_kv_heads * head_dim
+    q = x[:, :nq].view(T, n_heads, head_dim)
+    k = x[:, nq:nq + nk].view(T, n_kv_heads, head_dim)
+    v = x[:, nq + nk:].view(T, n_kv_heads, head_dim)
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    cos, sin = ang.cos(), ang.sin()
+    r = inv_freq.shape[0]
+    half = head_dim // 2
+
+    def rot(t):
+        t = t.clone()
+        x1, x2 = t[..., :r].clone(), t[..., half:half + r].clone()
+        t[..., :r] = x1 * cos[:, None, :] - x2 * sin[:, None, :]
+        t[..., half:half + r] = x2 * cos[:, None, :] + x1 * sin[:, None, :]
+        return t
+    qkv[:, :nq] = rot(q).reshape(T, nq).to(qkv.dtype)
+    if slots is not None:
+        kr = rot(k)
+        keep = slots >= 0
+        s = slots[keep].long()
+        page, off = s // page_size, s % page_size
+        k_pages[page, :, off, :] = kr[keep].to(k_pages.dtype)
+        v_pages[page, :, off, :] = v[keep].to(v_pages.dtype)
+
+
+def attention_scratch_floats(T, n_heads, head_dim, n_splits):
+    return 0 if n_splits <= 1 else T * n_heads * n_splits * (head_dim + 2)
+
+
+def paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads,
+                    head_dim, page_size, window, scale, n_splits=1, scratch=None):
+    T = q.shape[0]
+    g = n_heads // n_kv_heads
+    for t in range(T):
+        p = int(positions[t])
+        if p < 0:
+            out[t] = 0
+            continue
+        lo = max(0, p + 1 - window) if window else 0
+        n = torch.arange(lo, p + 1)
+        pages = block_table[int(tok_seg[t])].long()[n // page_size]
+        k = k_pages[pages, :, n % page_size, :].float()    # [keys, kv_heads, hd]
+        v = v_pages[pages, :, n % page_size, :].float()
+        qt = q[t, :n_heads * head_dim].float().view(n_heads, head_dim)
+        for h in range(n_heads):
+            s = (k[:, h // g, :] @ qt[h]) * scale
+            pr = torch.softmax(s, dim=0)
+            out[t, h * head_dim:(h + 1) * head_dim] = (pr @ v[:, h // g, :]).to(out.dtype)
+    return out
+
+
+def linear(x, weight, out=None):
+    y = (x.float() @ weight.float().t()).to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def logits_linear(x, weight):
+    return x.float() @ weight.float().t()
+
+
+def sample(logits, temperature, top_p, uniform, out):
+    R, V = logits.shape
+    for r in range(R):
+        t = 0.0 if temperature is None else float(temperature[r])
+        if t <= 0:
+            out[r] = int(torch.argmax(logits[r]))
+            continue
+        probs = plain.softmax_temperature(logits[r].double(), t)
+        tp = 1.0 if top_p is None else float(top_p[r])
+        if tp < 1.0:
+            probs = plain.top_p_filter(probs[None], tp)[0]
+        cum = torch.cumsum(probs, 0)
+        idx = int(torch.searchsorted(cum, torch.tensor(float(uniform[r]) * float(cum[-1]), dtype=cum.dtype),
+                                     right=True))
+        out[r] = min(idx, V - 1)
+    return out
+
+
+NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
+         "linear", "logits_linear", "sample"]
+
+
+def install(monkeypatch):
+    """Replaces the kernels of pico_vllm_b200.ops with the doubles above."""
+    import pico_vllm_b200.ops as ops
+    for name in NAMES:
+        monkeypatch.setattr(ops, name, globals()[name])
