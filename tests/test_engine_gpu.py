@@ -1,0 +1,282 @@
+"""The engine on the GPU against the plain implementation, in 32-bit and in bfloat16: every
+way of cutting requests into steps, long decoding, first tokens, generation through the entry
+point, graph replay, parts alone, and a toy mixer with state of its own."""
+import math
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+REL = {"float32": 5e-5, "bfloat16": 3e-2}     # max |difference| / max |logit| over a step
+LENGTHS = {"a": [5, 17, 33, 70, 150], "b": [1, 9, 24, 40, 77, 131], "c": [3, 21, 50, 97]}
+
+
+def _requests(name, vocab):
+    return {f"r{i}": helpers.random_ids(n, vocab, 1000 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+def _plain_logits(name, reqs, tensors):
+    cfg = helpers.tiny_config(name)
+    return {rid: plain.forward(ids, tensors, helpers.plain_config(cfg)) for rid, ids in reqs.items()}
+
+
+_CUTS = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_tail_decode(r, 32),
+         "portions": helpers.trace_portions, "mixed": helpers.trace_mixed}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("graph", [False, True])
+def test_every_cutting_matches_plain(dtype, name, cut, graph):
+    if graph and cut in ("whole", "portions"):
+        pytest.skip("no single-token steps in this cutting")
+    cfg = helpers.tiny_config(name)
+    reqs = _requests(name, cfg.vocab_size)
+    steps = _CUTS[cut](reqs)
+    runner, tensors = helpers.make_runner_from_tensors(name, dtype, DEV, helpers.live_token_peak(steps),
+                                                       use_cuda_graph=graph)
+    want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
+    got = helpers.replay(runner, steps)
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert (g is None) == (w is None)
+        if w is not None:
+            assert torch.isfinite(g).all(), f"{name}/{cut} step {i}: not finite (a freed page was read?)"
+            helpers.assert_close_logits(g, w, REL[dtype], f"{name}/{cut}/{dtype} step {i}")
+    if graph:
+        assert runner.graph_replays > 0
+    assert all(g.pool.in_use == 0 for g in runner.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_long_decoding(dtype, name):
+    """A short prompt, then 400 tokens one by one (pages fill up, the window moves on)."""
+    cfg = helpers.tiny_config(name)
+    ids = helpers.random_ids(420, cfg.vocab_size, 77)
+    reqs = {"x": ids}
+    steps = helpers.trace_tail_decode(reqs, 400)
+    runner, tensors = helpers.make_runner_from_tensors(name, dtype, DEV, 448, use_cuda_graph=True)
+    want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
+    got = helpers.replay(runner, steps)
+    for i, (g, w) in enumerate(zip(got, want)):
+        helpers.assert_close_logits(g, w, REL[dtype], f"{name}/{dtype} step {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(dtype):
+    """Position 0 alone, then 1, 2, 3 one by one: the shortest contexts."""
+    cfg = helpers.tiny_config("c")
+    reqs = {"x": helpers.random_ids(6, cfg.vocab_size, 5)}
+    steps = helpers.trace_tail_decode(reqs, 5)
+    runner, tensors = helpers.make_runner_from_tensors("c", dtype, DEV, 64)
+    want = helpers.expected_logits(steps, reqs, _plain_logits("c", reqs, tensors))
+    for i, (g, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+        helpers.assert_close_logits(g, w, REL[dtype], f"step {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_key_among_hundreds_and_page_edges(dtype):
+    """Weights are random, so a far key would hardly matter: instead the first layer's query and
+    key projections are scaled up, which makes attention sharp and every key position count."""
+    name = "a"
+    cfg = helpers.tiny_config(name)
+    from pico_vllm_b200.config import EngineConfig
+    from pico_vllm_b200.engine import ModelRunner, make_cache, model_from_tensors
+    tensors = helpers.tiny_tensors(name, torch.float32 if dtype == "float32" else torch.bfloat16)
+    for k in ("q_proj", "k_proj"):
+        tensors[f"model.layers.0.self_attn.{k}.weight"] = tensors[f"model.layers.0.self_attn.{k}.weight"] * 12
+        tensors[f"model.layers.0.self_attn.{k}.bias"] = tensors[f"model.layers.0.self_attn.{k}.bias"] * 12
+    ecfg = EngineConfig(dtype=dtype, page_size=16, max_cache_tokens=640, max_num_seqs=2, use_cuda_graph=False,
+                        device=DEV)
+    model = model_from_tensors(cfg, tensors, ecfg)
+    runner = ModelRunner(model, make_cache(model, ecfg, poison_freed=True), ecfg)
+    reqs = {"x": helpers.random_ids(600, cfg.vocab_size, 9)}
+    # portions that end exactly on, one before and one after page edges
+    sizes = (16, 15, 1, 17, 31, 2, 48, 63, 65, 128, 2, 212)
+    steps = helpers.trace_portions(reqs, sizes)
+    want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
+    for i, (g, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+        helpers.assert_close_logits(g, w, REL[dtype] * (1 if dtype == "float32" else 2), f"step {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(dtype, tmp_path):
+    from pico_vllm_b200 import LLM, SamplingParams
+    name = "b"
+    cfg = helpers.tiny_config(name)
+    helpers.write_tiny_model(name, tmp_path, dtype=dtype)
+    llm = LLM(str(tmp_path), dtype=dtype, device=DEV, page_size=8, num_pages=40, max_num_seqs=4,
+              max_num_batched_tokens=32, prefill_chunk=7, max_model_len=128)
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 50 + n) for n in (1, 9, 24, 40, 13, 30)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True))
+    tensors = helpers.tiny_tensors(name, torch.float32 if dtype == "float32" else torch.bfloat16)
+    pcfg = helpers.plain_config(cfg)
+    for p, o in zip(prompts, outs):
+        if dtype == "float32":
+            assert o.token_ids == plain.greedy_generate(p, tensors, pcfg, 12)
+        else:
+            # bfloat16 may pick another token where two logits are close: follow the engine's own
+            # tokens and require that each was (nearly) the plain implementation's best
+            ids = list(p) + o.token_ids
+            logits = plain.forward(ids, tensors, pcfg)
+            for j, tok in enumerate(o.token_ids):
+                row = logits[len(p) + j - 1]
+                assert float(row.max() - row[tok]) <= 3e-2 * float(row.abs().max())
+    llm.cache.check()
+    assert all(g.pool.in_use == 0 for g in llm.cache.groups)
+
+
+def test_sampling_through_the_entry_point_is_reproducible(tmp_path):
+    from pico_vllm_b200 import LLM, SamplingParams
+    helpers.write_tiny_model("a", tmp_path, dtype="float32")
+    cfg = helpers.tiny_config("a")
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 90 + n) for n in (4, 11, 19)]
+    sp = SamplingParams(temperature=0.8, top_p=0.95, max_new_tokens=8, seed=11, ignore_eos=True)
+    a = LLM(str(tmp_path), dtype="float32", device=DEV, max_cache_tokens=512).generate(prompts, sp)
+    llm2 = LLM(str(tmp_path), dtype="float32", device=DEV, max_cache_tokens=512, max_num_batched_tokens=5)
+    b = [llm2.generate([p], sp)[0] for p in prompts]
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    assert len({tuple(o.token_ids) for o in a}) > 1
+
+
+# ------------------------------------------------------------------ parts alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    """Norm, feed-forward and attention parts, each built by itself with sizes of its own."""
+    from pico_vllm_b200.parts import GQAAttention, GatedMLP, RMSNorm, Rotary, CacheView
+    from pico_vllm_b200.engine.batch import Batch, GroupBatch
+    g = torch.Generator().manual_seed(1)
+    t = dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    W, T = 72, 11
+    # norm
+    norm = RMSNorm(W, 1e-4)
+    norm.materialize(DEV, dtype)
+    norm.weight = (1 + 0.1 * torch.randn(W, generator=g)).to(DEV)
+    x = torch.randn(T, W, generator=g)
+    d = torch.randn(T, W, generator=g).to(dtype)
+    xg = x.to(DEV)
+    y = norm.add_norm(xg, d.to(DEV))
+    want = plain.rms_norm(x + d.float(), norm.weight.cpu(), 1e-4)
+    assert torch.allclose(y.cpu().float(), want, **t)
+    # feed-forward
+    mlp = GatedMLP(W, 100)
+    wg, wu, wd = (torch.randn(100, W, generator=g) * 0.1, torch.randn(100, W, generator=g) * 0.1,
+                  torch.randn(W, 100, generator=g) * 0.1)
+    mlp.gate_up_weight = torch.cat([wg, wu]).to(dtype).to(DEV)
+    mlp.down_weight = wd.to(dtype).to(DEV)
+    h = torch.randn(T, W, generator=g).to(dtype)
+    got = mlp.forward(h.to(DEV), None).cpu().float()
+    w = {"gate_proj.weight": wg.to(dtype).float(), "up_proj.weight": wu.to(dtype).float(),
+         "down_proj.weight": wd.to(dtype).float()}
+    assert torch.allclose(got, plain.swiglu_mlp(h.float(), w, ""), **t)
+    # attention: one request, 11 tokens at once, against the plain whole-sequence attention
+    nh, nkv, hd, ps = 6, 2, 16, 4
+    attn = GQAAttention(W, nh, nkv, hd, position=Rotary(hd, 777.0), window=5)
+    attn.materialize(DEV, dtype)
+    ws = {n: torch.randn(o, W, generator=g) * 0.2 for n, o in (("q", nh * hd), ("k", nkv * hd), ("v", nkv * hd))}
+    bs = {n: torch.randn(ws[n].shape[0], generator=g) * 0.2 for n in "qkv"}
+    wo = torch.randn(W, nh * hd, generator=g) * 0.2
+    attn.qkv_weight = torch.cat([ws["q"], ws["k"], ws["v"]]).to(dtype).to(DEV)
+    attn.qkv_bias = torch.cat([bs["q"], bs["k"], bs["v"]]).to(DEV)
+    attn.o_weight = wo.to(dtype).to(DEV)
+    pages = torch.zeros(2, 8, nkv, ps, hd, dtype=dtype, device=DEV)
+    table = torch.tensor([[5, 2, 7, 0]], dtype=torch.int32, device=DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = (table[0].long()[pos.long() // ps] * ps + pos.long() % ps).to(torch.int32)
+    zero = torch.zeros(T, dtype=torch.int32, device=DEV)
+    batch = Batch(T, 1, zero, pos, zero, zero[:1], zero[:2], zero[:0], 0, {0: GroupBatch(slots, table)}, [T], [T])
+    got = attn.forward(h.to(DEV), batch, CacheView(group=0, k=pages[0], v=pages[1], page_size=ps)).cpu().float()
+    pw = {f"{n}_proj.weight": ws[n].to(dtype).float() for n in "qkv"}
+    pw.update({f"{n}_proj.bias": bs[n] for n in "qkv"})
+    pw["o_proj.weight"] = wo.to(dtype).float()
+    pcfg = dict(num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, rope_theta=777.0)
+    want = plain.attention_block(h.float(), pw, "", torch.arange(T), pcfg, 5)
+    assert torch.allclose(got, want, **t)
+
+
+# ------------------------------------------------------------------ a toy mixer with state of its own
+def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped():
+    """A mixer defined here - a decaying running mean of its inputs, kept per request in a
+    fixed-size state slot - is registered, put into a model next to attention layers and stepped
+    in portions and mixed batches, without any change to the package."""
+    from pico_vllm_b200.parts import (Part, Param, Piece, FixedState, register, make, PreNormBlock, RMSNorm,
+                                      GatedMLP, GQAAttention, Rotary, TokenEmbedding, OutputHead)
+    from pico_vllm_b200.models import DecoderModel, LayerCall, Binding
+    from pico_vllm_b200.config import EngineConfig
+    from pico_vllm_b200.engine import ModelRunner, StepItem, make_cache
+    from pico_vllm_b200.weights import load_state_dict
+
+    @register("mixer", "toy_running_mean")
+    class RunningMean(Part):
+        def __init__(self, width, decay):
+            self.width, self.decay = width, decay
+            self.mix = None
+
+        def params(self):
+            return [Param("mix", (Piece("mix", (self.width, self.width)),))]
+
+        def cache_spec(self):
+            return FixedState((self.width,), "float32")
+
+        def forward(self, h, batch, cache):
+            out = torch.empty_like(h)
+            at = 0
+            slots = batch.seg_slots.tolist()
+            for s, n in enumerate(batch.q_lens):           # tokens of a segment in order
+                state = cache.state[slots[s]]
+                for i in range(at, at + n):
+                    state.mul_(self.decay).add_(h[i].float() * (1 - self.decay))
+                    out[i] = state.to(h.dtype)
+                at += n
+            return out @ self.mix.t()
+
+    W, V = 32, 50
+    embed = TokenEmbedding(V, W)
+    toy = make("mixer", "toy_running_mean", width=W, decay=0.75)
+    attn = GQAAttention(W, 2, 1, 16, position=Rotary(16, 100.0))
+    blocks = [PreNormBlock(RMSNorm(W, 1e-5), toy, RMSNorm(W, 1e-5), GatedMLP(W, 48)),
+              PreNormBlock(RMSNorm(W, 1e-5), attn, RMSNorm(W, 1e-5), GatedMLP(W, 48))]
+    names = []
+    bindings = [Binding(embed, {"weight": "emb"})]
+    for i, b in enumerate(blocks):
+        for pn, part in b.parts().items():
+            bindings.append(Binding(part, {pc.key: f"l{i}.{pn}.{pc.key}" for p in part.params() for pc in p.pieces}))
+    fn = RMSNorm(W, 1e-5)
+    bindings.append(Binding(fn, {"weight": "fn"}))
+    head = OutputHead(V, W, tied_to=embed)
+    # the order names the attention block twice: its second call has a cache entry of its own
+    order = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(1, 2)]
+
+    class Cfg:
+        architecture = "ToyForTest"
+        max_position_embeddings = 256
+    model = DecoderModel(Cfg(), embed, blocks, order, fn, head, bindings)
+    g = torch.Generator().manual_seed(3)
+    tensors = {}
+    for b in bindings:
+        for p in b.part.params():
+            for pc in p.pieces:
+                t = torch.randn(pc.shape, generator=g) * 0.3
+                tensors[b.names[pc.key]] = t + 1 if p.init == "one_plus_normal" else t
+    ecfg = EngineConfig(dtype="float32", page_size=4, max_cache_tokens=256, max_num_seqs=3, use_cuda_graph=False,
+                        device=DEV)
+    load_state_dict(model, tensors, torch.float32, DEV)
+    model.materialize(DEV, torch.float32)
+    runner = ModelRunner(model, make_cache(model, ecfg), ecfg)
+    ids = {"p": helpers.random_ids(23, V, 1), "q": helpers.random_ids(14, V, 2)}
+    whole = helpers.replay(runner, helpers.trace_whole(ids))
+    ref = {"p": whole[0], "q": whole[1]}
+    steps = helpers.trace_mixed(ids, max_live=2, seed=4, chunk_sizes=(3, 2, 5))
+    want = helpers.expected_logits(steps, ids, ref)
+    for i, (gg, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+        helpers.assert_close_logits(gg, w, 5e-5, f"toy step {i}")
+    # the state really matters: another decay gives other logits
+    toy.decay = 0.5
+    other = helpers.replay(runner, helpers.trace_whole({"p": ids["p"]}))[0]
+    assert float((other - ref["p"]).abs().max()) > 1e-3

@@ -1,0 +1,229 @@
+"""Each CUDA kernel alone against its plain float32 reference (tests/fake_ops.py), at sizes
+other than the engine's tiny and benchmark configurations."""
+import math
+
+import pytest
+import torch
+
+import fake_ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+@pytest.mark.parametrize("tdtype", DTYPES)
+@pytest.mark.parametrize("T,H,V", [(1, 16, 7), (37, 200, 331), (5, 1000, 50)])
+def test_embedding(tdtype, T, H, V):
+    from pico_vllm_b200 import ops
+    table = torch.randn(V, H, generator=gen(1)).to(tdtype)
+    ids = torch.randint(0, V, (T,), generator=gen(2), dtype=torch.int32)
+    out = torch.empty(T, H, dtype=torch.float32, device=DEV)
+    ops.embedding(ids.to(DEV), table.to(DEV), out)
+    want = fake_ops.embedding(ids, table, torch.empty(T, H))
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,eps", [(1, 16, 1e-6), (9, 200, 1e-5), (4, 1000, 1e-3), (3, 5000, 1e-6)])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_add_rmsnorm(dtype, T, H, eps, with_delta):
+    from pico_vllm_b200 import ops
+    x = torch.randn(T, H, generator=gen(3)) * 3
+    d = (torch.randn(T, H, generator=gen(4))).to(dtype) if with_delta else None
+    w = 1 + 0.1 * torch.randn(H, generator=gen(5))
+    xg = x.to(DEV)
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(xg, None if d is None else d.to(DEV), w.to(DEV), eps, out)
+    xr = x.clone()
+    want = fake_ops.add_rmsnorm(xr, d, w, eps, torch.empty(T, H, dtype=dtype))
+    assert torch.allclose(out.cpu().float(), want.float(), **tol(dtype))
+    assert torch.allclose(xg.cpu(), xr, atol=1e-6)            # the residual stream was updated in place
+    # rows: norm of chosen rows, residual untouched
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32)
+    x2 = x.to(DEV)
+    out2 = torch.empty(2, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(x2, None if d is None else d.to(DEV), w.to(DEV), eps, out2, rows.to(DEV))
+    want2 = fake_ops.add_rmsnorm(x.clone(), d, w, eps, torch.empty(2, H, dtype=dtype), rows)
+    assert torch.allclose(out2.cpu().float(), want2.float(), **tol(dtype))
+    assert torch.equal(x2.cpu(), x)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 8), (7, 176), (33, 1000)])
+def test_swiglu(dtype, T, I):
+    from pico_vllm_b200 import ops
+    gu = (torch.randn(T, 2 * I, generator=gen(6)) * 4).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops.swiglu(gu.to(DEV), out)
+    want = fake_ops.swiglu(gu, torch.empty(T, I, dtype=dtype))
+    assert torch.allclose(out.cpu().float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps,rot", [(4, 2, 16, 16, 16), (6, 3, 32, 8, 32), (5, 1, 48, 4, 48),
+                                              (3, 3, 80, 16, 40), (2, 1, 128, 32, 0)])
+def test_rope_store(dtype, nh, nkv, hd, ps, rot):
+    from pico_vllm_b200 import ops
+    T, pages = 19, 12
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, generator=gen(7)).to(dtype)
+    bias = 0.5 * torch.randn(width, generator=gen(8))
+    pos = torch.randint(0, 5000, (T,), generator=gen(9), dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2).float() / max(rot, 1))) if rot else torch.zeros(0)
+    slots = torch.randperm(pages * ps, generator=gen(10))[:T].to(torch.int32)
+    slots[3] = -1
+    k0 = torch.randn(pages, nkv, ps, hd, generator=gen(11)).to(dtype)
+    v0 = torch.randn(pages, nkv, ps, hd, generator=gen(12)).to(dtype)
+    qg, kg, vg = qkv.to(DEV), k0.to(DEV), v0.to(DEV)
+    ops.rope_store(qg, bias.to(DEV), pos.to(DEV), inv.to(DEV), slots.to(DEV), kg, vg, nh, nkv, hd, ps)
+    qr, kr, vr = qkv.clone(), k0.clone(), v0.clone()
+    fake_ops.rope_store(qr, bias, pos, inv, slots, kr, vr, nh, nkv, hd, ps)
+    t = dict(atol=3e-4, rtol=1e-4) if dtype == torch.float32 else tol(dtype)   # angles up to 5000 rad
+    assert torch.allclose(qg.cpu().float()[:, :nh * hd], qr.float()[:, :nh * hd], **t)
+    assert torch.allclose(kg.cpu().float(), kr.float(), **t)
+    assert torch.allclose(vg.cpu().float(), vr.float(), **t)
+    # without slots only q is rotated and the pages stay as they were
+    qg2, kg2 = qkv.to(DEV), k0.to(DEV)
+    ops.rope_store(qg2, bias.to(DEV), pos.to(DEV), inv.to(DEV), None, None, None, nh, nkv, hd, ps)
+    assert torch.allclose(qg2.cpu().float()[:, :nh * hd], qr.float()[:, :nh * hd], **t)
+
+
+def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, seed=0, spike=False):
+    """Segments with kv lengths seg_lens, of which the last q_lens are this step's queries."""
+    from pico_vllm_b200 import ops
+    g = gen(20 + seed)
+    S = len(seg_lens)
+    blocks = [-(-n // ps) for n in seg_lens]
+    pages = sum(blocks) + 3
+    perm = torch.randperm(pages, generator=g).tolist()
+    W = max(blocks) + 1
+    table = torch.zeros(S, W, dtype=torch.int32)
+    at = 0
+    for s, b in enumerate(blocks):
+        table[s, :b] = torch.tensor(perm[at:at + b], dtype=torch.int32)
+        at += b
+    k = torch.randn(pages, nkv, ps, hd, generator=g).to(dtype)
+    v = torch.randn(pages, nkv, ps, hd, generator=g).to(dtype)
+    T = sum(q_lens)
+    q = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    tok_seg = torch.cat([torch.full((n,), s, dtype=torch.int32) for s, n in enumerate(q_lens)])
+    pos = torch.cat([torch.arange(L - n, L, dtype=torch.int32) for L, n in zip(seg_lens, q_lens)])
+    if spike:
+        # one far key gets a score that dwarfs the rest: a kernel that skips it, or reads the wrong
+        # page for it, gives a visibly different output
+        for s, L in enumerate(seg_lens):
+            far = 1 if window is None else max(0, L - window)       # first visible key of the last query
+            pg, off = table[s, far // ps], far % ps
+            t_last = int((tok_seg == s).nonzero()[-1])
+            qv = q[t_last, :hd].float()
+            k[pg, 0, off, :] = (qv / qv.norm() * 30).to(dtype)
+            q[t_last, :hd] = (qv / qv.norm() * 6).to(dtype)
+    out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(ops.attention_scratch_floats(T, nh, hd, splits), dtype=torch.float32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(q.to(DEV), k.to(DEV), v.to(DEV), out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
+                        nh, nkv, hd, ps, window, scale, splits, scratch)
+    want = torch.empty(T, nh * hd, dtype=dtype)
+    fake_ops.paged_attention(q, k, v, want, tok_seg, pos, table, nh, nkv, hd, ps, window, scale)
+    return out.cpu().float(), want.float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 16), (6, 3, 32, 8), (5, 1, 48, 4), (12, 2, 128, 16),
+                                          (3, 3, 80, 16), (8, 1, 256, 32)])
+@pytest.mark.parametrize("window", [None, 24])
+def test_paged_attention_mixed_segments(dtype, nh, nkv, hd, ps, window):
+    # a long prompt portion, a decode token with a long context, a short one, a first token
+    got, want = _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens=[70, 133, 9, 1], q_lens=[33, 1, 2, 1],
+                                splits=1)
+    assert torch.allclose(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [2, 5, 16])
+@pytest.mark.parametrize("window", [None, 100])
+def test_paged_attention_split_keys(dtype, splits, window):
+    got, want = _attention_case(dtype, 6, 2, 64, 16, window, seg_lens=[700, 333, 40, 3], q_lens=[1, 1, 1, 1],
+                                splits=splits, seed=3)
+    assert torch.allclose(got, want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window,splits", [(None, 1), (None, 8), (64, 1), (64, 4)])
+def test_paged_attention_far_key_and_window_edge(dtype, window, splits):
+    got, want = _attention_case(dtype, 4, 2, 32, 8, window, seg_lens=[517, 300], q_lens=[1, 2], splits=splits,
+                                seed=5, spike=True)
+    assert torch.allclose(got, want, **tol(dtype))
+
+
+def test_refuses_head_sizes_it_does_not_take():
+    from pico_vllm_b200 import ops
+    from pico_vllm_b200.errors import KernelError
+    q = torch.zeros(1, 3 * 24, device=DEV)
+    kv = torch.zeros(2, 1, 4, 24, device=DEV)
+    i = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError):
+        ops.paged_attention(q, kv, kv, torch.zeros(1, 24, device=DEV), i, i, torch.zeros(1, 2, dtype=torch.int32,
+                            device=DEV), 1, 1, 24, 4, None, 1.0)
+    with pytest.raises(KernelError):
+        ops.embedding(torch.zeros(1, dtype=torch.int32), torch.zeros(2, 2), torch.zeros(1, 2))   # CPU tensors
+
+
+@pytest.mark.parametrize("V", [50, 331, 5000, 151936])
+def test_sample_greedy_and_temperature(V):
+    from pico_vllm_b200 import ops
+    R = 6
+    logits = torch.randn(R, V, generator=gen(30)) * 3
+    logits[1, V // 2] = logits[1].max() + 1      # a clear winner
+    logits[2, 3] = logits[2, 7] = logits[2].max() + 1   # a tie: the lower index wins
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), None, None, None, out)
+    want = torch.empty(R, dtype=torch.int32)
+    fake_ops.sample(logits, None, None, None, want)
+    assert out.cpu().tolist() == want.tolist()
+    assert out[2].item() == 3
+    # temperature / top-p rows mixed with a greedy row
+    temp = torch.tensor([0.0, 0.7, 1.0, 1.3, 0.8, 2.0])
+    topp = torch.tensor([1.0, 1.0, 0.9, 0.5, 0.2, 1.0])
+    for trial in range(4):
+        u = torch.rand(R, generator=gen(40 + trial))
+        ops.sample(logits.to(DEV), temp.to(DEV), topp.to(DEV), u.to(DEV), out)
+        got = out.cpu().tolist()
+        for r in range(R):
+            if temp[r] == 0:
+                assert got[r] == int(torch.argmax(logits[r]))
+                continue
+            probs = torch.softmax(logits[r].double() / float(temp[r]), 0)
+            if topp[r] < 1:
+                import plain_qwen2 as plain
+                probs = plain.top_p_filter(probs[None], float(topp[r]))[0]
+            assert probs[got[r]] > 0, "a token outside the top-p set was drawn"
+            cum = torch.cumsum(probs, 0)
+            lo = float(cum[got[r]] - probs[got[r]])
+            hi = float(cum[got[r]])
+            target = float(u[r]) * float(cum[-1])
+            assert lo - 1e-4 <= target <= hi + 1e-4, (r, lo, target, hi)
+
+
+def test_sample_distribution():
+    from pico_vllm_b200 import ops
+    V, N = 7, 4000
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5, 3.0, -5.0]]).repeat(N, 1)
+    u = torch.rand(N, generator=gen(50))
+    out = torch.empty(N, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), torch.full((N,), 1.5).to(DEV), torch.ones(N).to(DEV), u.to(DEV), out)
+    freq = torch.bincount(out.cpu().long(), minlength=V).double() / N
+    probs = torch.softmax(logits[0].double() / 1.5, 0)
+    assert float((freq - probs).abs().max()) < 0.03

@@ -1,0 +1,70 @@
+"""The entry point, scheduler and sampler wiring on the CPU with kernel doubles."""
+import torch
+
+import fake_ops
+import helpers
+import plain_qwen2 as plain
+
+
+def _llm(monkeypatch, tmp_path, name, **opts):
+    fake_ops.install(monkeypatch)
+    from pico_vllm_b200 import LLM
+    helpers.write_tiny_model(name, tmp_path, dtype="float32")
+    return LLM(str(tmp_path), dtype="float32", device="cpu", use_cuda_graph=False,
+               page_size=helpers.TINY[name]["page_size"], **opts)
+
+
+def test_greedy_generation_equals_plain(monkeypatch, tmp_path):
+    from pico_vllm_b200 import SamplingParams
+    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=512)
+    cfg = helpers.tiny_config("a")
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 7 + n) for n in (5, 17, 33)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True))
+    tensors = helpers.tiny_tensors("a", torch.float32)
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain.greedy_generate(p, tensors, helpers.plain_config(cfg), 8)
+        assert o.finish_reason == "length"
+    llm.cache.check()
+    assert all(g.pool.in_use == 0 for g in llm.cache.groups)
+
+
+def test_chunked_prefill_with_preemption_gives_the_same_tokens(monkeypatch, tmp_path):
+    from pico_vllm_b200 import SamplingParams
+    # 9 requests, few pages, portions of 7 tokens: requests are pre-empted and recomputed
+    llm = _llm(monkeypatch, tmp_path, "b", num_pages=14, max_num_seqs=4, max_num_batched_tokens=16,
+               prefill_chunk=7, max_model_len=112)
+    cfg = helpers.tiny_config("b")
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 50 + n) for n in (1, 9, 24, 40, 13, 30, 6, 21, 35)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=10, ignore_eos=True))
+    tensors = helpers.tiny_tensors("b", torch.float32)
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain.greedy_generate(p, tensors, helpers.plain_config(cfg), 10)
+    assert llm.scheduler.num_preemptions > 0
+    llm.cache.check()
+
+
+def test_submit_step_calls_of_the_reference(monkeypatch, tmp_path):
+    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=256)
+    a = llm.submit([1, 2, 3], max_new_tokens=3, temperature=0, top_p=1.0, ignore_eos=True)
+    b = llm.submit([4, 5], max_new_tokens=5, temperature=0.8, top_p=0.9, seed=3, ignore_eos=True)
+    llm.mark_finished()
+    assert llm.submit([1], 1, 0, 1.0) == -1
+    got = {}
+    while not llm.is_done():
+        for rid, ids in llm.step():
+            got[rid] = ids
+    assert len(got[a]) == 3 + 3 and got[a][:3] == [1, 2, 3]
+    assert len(got[b]) == 2 + 5
+
+
+def test_sampled_tokens_do_not_depend_on_batching(monkeypatch, tmp_path):
+    from pico_vllm_b200 import SamplingParams
+    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=512)
+    cfg = helpers.tiny_config("a")
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 90 + n) for n in (4, 11, 19)]
+    sp = SamplingParams(temperature=0.8, top_p=0.95, max_new_tokens=6, seed=11, ignore_eos=True)
+    together = llm.generate(prompts, sp)
+    # the same request ids (0, 1, 2) one at a time in a fresh engine
+    llm2 = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=512)
+    alone = [llm2.generate([p], sp)[0] for p in prompts]
+    assert [o.token_ids for o in together] == [o.token_ids for o in alone]
