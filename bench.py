@@ -1,0 +1,346 @@
+"""Benchmark of the serving step: decode tokens per second on one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of the Qwen2.5-1.5B shape (28 layers, width 1536, 12 query and 2
+key/value heads of 128, feed-forward 8960, vocabulary 151936, tied head) with random weights,
+bfloat16, a batch of 8 requests decoding at a context of 4096 tokens.  A "step" is one decode
+step of the whole batch.  Prints ONE JSON line:
+
+* ``value``: decoded tokens per second, timed on the device with CUDA events around K steps of
+  the step function (batch building, index upload and graph replay included);
+* ``e2e``: the same through the Python entry point (``LLM.submit`` / ``LLM.step``), host token
+  ids in, sampled host token ids out, every step;
+* ``prefill``: one 2,048-token prompt through the step function;
+* ``roofline``: bytes a decode step has to read (every weight once, the cache of the live
+  requests) / its time, against the measured copy bandwidth;
+* ``points``: decode tokens per second at batch 1 and 64.
+
+The weights and the cache of every timed step are far larger than the 126 MB L2, so no L2 flush
+is needed between iterations (``config.l2`` says so).  Peaks come from MEASURED_PEAKS.json when
+the file is there, else from the fallback of an earlier measurement on this kind of GPU.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+PUBLISHED_DECODE_B1 = 97.0   # tok/s, batch 1, the reference's README (other hardware)
+
+MODEL = dict(architectures=["Qwen2ForCausalLM"], vocab_size=151936, hidden_size=1536, num_hidden_layers=28,
+             num_attention_heads=12, num_key_value_heads=2, intermediate_size=8960, rope_theta=1000000.0,
+             rms_norm_eps=1e-6, tie_word_embeddings=True, use_sliding_window=False,
+             max_position_embeddings=32768, hidden_act="silu")
+FULL_LAYERS = 28
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+    try:
+        with open(path) as f:
+            m = json.load(f)
+        if "hbm_gbs" in m:
+            out["hbm_gbs"] = float(m["hbm_gbs"])
+        if "bf16_tflops" in m:
+            out["bf16_tflops"] = float(m["bf16_tflops"])
+        if "bf16_tflops_sustained" in m:
+            out["bf16_tflops_sustained"] = float(m["bf16_tflops_sustained"])
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi in the background, sampling SM clock and throttle reasons every 200 ms."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                    power.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.remove(self.path)
+        except OSError:
+            pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def scratch_dir(need_bytes):
+    """A memory-backed folder when it has room (the model folder is written and read once)."""
+    try:
+        st = os.statvfs("/dev/shm")
+        if st.f_bavail * st.f_frsize > need_bytes and os.access("/dev/shm", os.W_OK):
+            return "/dev/shm"
+    except OSError:
+        pass
+    return None
+
+
+def make_model_folder(layers, folder):
+    import torch
+    from pico_vllm_b200.registry import config_from_dict
+    from pico_vllm_b200.weights import write_random_model
+    raw = dict(MODEL, num_hidden_layers=layers)
+    cfg = config_from_dict(raw)
+    t0 = time.time()
+    write_random_model(cfg, seed=0, out_dir=folder, dtype="bfloat16")
+    print(f"[bench] random {layers}-layer model written in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    return cfg
+
+
+def weight_bytes(model):
+    """Bytes of every weight a decode step reads once (the embedding table counts once: it is
+    the head's matrix when tied; the gather of a few rows is left out)."""
+    seen, total = set(), 0
+    for part in model.all_parts():
+        for p in part.params():
+            t = getattr(part, p.attr)
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+    return total
+
+
+def kv_bytes_per_token(model, cache):
+    return cache.bytes_per_page() // cache.page_size
+
+
+def prefill_flops(cfg, T):
+    H, I, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    per_tok = 2 * (H * (nh + 2 * nkv) * hd + nh * hd * H + 2 * H * I + I * H)
+    attn = 4 * nh * hd * T * (T + 1) / 2          # q.k and p.v over the causal triangle
+    return L * (per_tok * T + attn) + 2 * H * V     # the head runs for one row
+
+
+def decode_phase(llm, batch, context, steps, warmup, seed):
+    """Fills ``batch`` requests up to (context - steps - warmup) tokens, then times ``steps``
+    decode steps on the device.  Returns (ms per step, launches per step, bytes uploaded per step)."""
+    import torch
+    from pico_vllm_b200 import ops
+    from pico_vllm_b200.engine import StepItem
+    runner, cache = llm.runner, llm.cache
+    V = llm.model.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    prompt_len = context - steps - warmup
+    slots = [cache.acquire(f"bench{i}") for i in range(batch)]
+    for s in slots:                                  # prompts in portions of 2048 tokens
+        at = 0
+        while at < prompt_len:
+            n = min(2048, prompt_len - at)
+            runner.step([StepItem(s, torch.randint(0, V, (n,), generator=g).tolist(), ())])
+            at += n
+    toks = torch.randint(0, V, (steps + warmup, batch), generator=g).tolist()
+    for i in range(warmup):
+        runner.step([StepItem(s, [toks[i][j]], (0,)) for j, s in enumerate(slots)])
+    torch.cuda.synchronize()
+    before = ops.launches
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(warmup, warmup + steps):
+        runner.step([StepItem(s, [toks[i][j]], (0,)) for j, s in enumerate(slots)])
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    launches = (ops.launches - before) / steps
+    for s in slots:
+        cache.release(s)
+    return ms, launches
+
+
+def e2e_phase(llm, batch, context, steps, warmup, seed):
+    """The same decode steps through LLM.submit / LLM.step: host ids in, sampled host ids out."""
+    import torch
+    V = llm.model.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    prompt_len = context - steps - warmup
+    for _ in range(batch):
+        llm.submit(torch.randint(0, V, (prompt_len,), generator=g).tolist(), max_new_tokens=steps + warmup + 64,
+                   temperature=0.0, top_p=1.0, ignore_eos=True)
+    while any(not r.is_decoding for r in llm.scheduler.running) or llm.scheduler.waiting:
+        llm.step()                                    # prompts, in portions
+    for _ in range(warmup - 1):
+        llm.step()
+    torch.cuda.synchronize()
+    t_start = time.perf_counter()
+    n = 0
+    for _ in range(steps):
+        llm.step()
+        n += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t_start
+    while llm.scheduler.has_work():
+        llm.step()
+    return dt * 1000.0 / n
+
+
+def prefill_phase(llm, T, reps, seed):
+    import torch
+    from pico_vllm_b200.engine import StepItem
+    runner, cache = llm.runner, llm.cache
+    V = llm.model.vocab_size
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, V, (T,), generator=g).tolist()
+    times = []
+    for i in range(reps + 3):
+        s = cache.acquire("prefill")
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0.record()
+        runner.step([StepItem(s, ids, (T - 1,))])
+        t1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(t0.elapsed_time(t1))
+        cache.release(s)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def run_ours(args):
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: bench.py needs a GPU"}))
+        return 1
+    import pico_vllm_b200  # noqa: F401
+    from pico_vllm_b200 import LLM, ops
+    pk = peaks()
+    batch, context = args.batch, args.context
+    layers = args.layers
+    tmp = tempfile.mkdtemp(prefix="pico_bench_", dir=scratch_dir(4 << 30))
+    try:
+        cfg = make_model_folder(layers, tmp)
+        max_b = max(64, batch) if not args.no_points else batch
+        pages = max_b * ((context + 128) // 16 + 1) + 256
+        llm = LLM(tmp, dtype="bfloat16", page_size=16, num_pages=pages, max_num_seqs=max_b,
+                  max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=context + 128,
+                  use_cuda_graph=True)
+    finally:
+        for f in os.listdir(tmp):
+            os.remove(os.path.join(tmp, f))
+        os.rmdir(tmp)
+    wbytes = weight_bytes(llm.model)
+    kvb = kv_bytes_per_token(llm.model, llm.cache)
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms, launches = decode_phase(llm, batch, context, args.steps, args.warmup, seed=1)
+    clocks = sampler.stop()
+
+    e2e_ms = e2e_phase(llm, batch, context, args.steps, args.warmup, seed=2)
+    T = 2048
+    pre_ms = prefill_phase(llm, T, reps=5, seed=3)
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _ = decode_phase(llm, b, context, 32, 8, seed=10 + b)
+            points[f"decode_b{b}"] = round(b / pms * 1000.0, 1)
+
+    step_bytes = wbytes + batch * (context - args.steps / 2) * kvb
+    achieved = step_bytes / (ms / 1000.0) / 1e9
+    flops = prefill_flops(cfg, T)
+    pre_frac = flops / (pre_ms / 1000.0) / (pk["bf16_tflops"] * 1e12)
+    value = batch / ms * 1000.0
+    stage = llm.runner._graphs[llm.runner._bucket(batch)]["buffers"].host.numel() * 4
+    out = {
+        "metric": "decode tok/s (Qwen2.5-1.5B shape, batch 8, context 4096)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-1.5B shape", "layers": layers, "layers_full": FULL_LAYERS,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "tied": cfg.tie_word_embeddings, "global_batch": batch, "seq_len": context,
+                   "page_size": 16, "parallelism": "single GPU", "cuda_graph": True,
+                   "l2": "no flush: each step reads >3 GB of weights and cache, L2 is 126 MB",
+                   "peaks": pk["source"]},
+        "clocks": clocks,
+        "e2e": {"value": round(batch / e2e_ms * 1000.0, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": stage, "d2h_bytes_per_step": 4 * batch},
+        "gpu_launches": int(round(launches * args.steps)),
+        "launches_per_step": round(launches, 1),
+        "prefill": {"value": round(T / pre_ms * 1000.0, 1), "tokens": T, "ms": round(pre_ms, 3),
+                    "frac": round(pre_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "decode_b1_vs_published_97": (round(points["decode_b1"] / PUBLISHED_DECODE_B1, 2)
+                                      if "decode_b1" in points else None),
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "the reference is not installable offline (pip: neither setup.py nor "
+                                         "pyproject.toml) and its engine needs the Qwen2.5-1.5B weights and "
+                                         "tokenizer from the network"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (this engine runs on a single GPU)")
+        return 2
+    args.warmup = max(args.warmup, 3)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
