@@ -197,3 +197,68 @@ PICO_API int pico_paged_attention_generic(const void* q, int q_row_stride, const
         return PICO_ERR_DTYPE;
     return pico_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and documented in pico_noalloc.h; it has no
+// counterpart in the reference).  Its scratch is this file-scope device array.  In host code the
+// name g_noalloc_scratch is only a stand-in for the symbol, not a device address: the address
+// the kernels get comes from cudaGetSymbolAddress, looked up once per device below.
+#include "pico_noalloc.h"
+#include <stdio.h>
+
+#define PICO_ERR_SCRATCH (-5)
+#define PICO_ERR_SYMBOL (-6)
+#define PICO_NOALLOC_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_noalloc_scratch[PICO_NOALLOC_SCRATCH_FLOATS];
+static float* g_noalloc_scratch_ptr[PICO_NOALLOC_MAX_DEVICES];   // device address, per device; 0 = not looked up
+
+static int noalloc_fail(int code, char* err, int err_len, const char* msg) {
+    if (err && err_len > 0) snprintf(err, (size_t)err_len, "pico_paged_attention_noalloc: %s", msg);
+    return code;
+}
+
+PICO_API int pico_paged_attention_noalloc(const void* q, int q_row_stride, const void* k_pages,
+                                          const void* v_pages, void* out, const int* tok_seg,
+                                          const int* positions, const int* block_table, int table_stride,
+                                          int T, int nh, int nkv, int hd, int page_size, int window, float scale,
+                                          int n_splits, int act_dtype, cudaStream_t stream, char* err,
+                                          int err_len) {
+    if (err && err_len > 0) err[0] = 0;
+    if (T <= 0) return 0;
+    if (nh <= 0 || hd <= 0 || n_splits < 1)
+        return noalloc_fail(PICO_ERR_SIZE, err, err_len, "nh, hd and n_splits must be positive");
+    const long long need = (long long)T * nh * n_splits * (hd + 2);
+    if (need > (long long)PICO_NOALLOC_SCRATCH_FLOATS) {
+        char msg[200];
+        snprintf(msg, sizeof msg,
+                 "T*nh*n_splits*(hd+2) = %lld float32 of scratch wanted, the built-in array holds %d "
+                 "(use fewer splits or tokens, or pico_paged_attention_generic with your own buffer)",
+                 need, (int)PICO_NOALLOC_SCRATCH_FLOATS);
+        return noalloc_fail(PICO_ERR_SCRATCH, err, err_len, msg);
+    }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PICO_NOALLOC_MAX_DEVICES)
+        return noalloc_fail(PICO_ERR_SYMBOL, err, err_len, "cannot tell the current device");
+    if (!g_noalloc_scratch_ptr[dev]) {
+        // set-up, once per device, with that device current
+        float* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            char msg[160];
+            snprintf(msg, sizeof msg, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return noalloc_fail(PICO_ERR_SYMBOL, err, err_len, msg);
+        }
+        g_noalloc_scratch_ptr[dev] = p;
+    }
+    float* part_o = g_noalloc_scratch_ptr[dev];
+    float* part_ml = part_o + (size_t)T * nh * n_splits * hd;
+    const int rc = pico_paged_attention_generic(q, q_row_stride, k_pages, v_pages, out, part_o, part_ml, tok_seg,
+                                                positions, block_table, table_stride, T, nh, nkv, hd, page_size,
+                                                window, scale, n_splits, act_dtype, stream);
+    if (rc == PICO_ERR_SIZE) return noalloc_fail(rc, err, err_len, "a size the attention kernels do not take");
+    if (rc == PICO_ERR_DTYPE) return noalloc_fail(rc, err, err_len, "act_dtype must be 0 (float32) or 1 (bfloat16)");
+    if (rc == PICO_ERR_ALIGN) return noalloc_fail(rc, err, err_len, "q_row_stride must be a multiple of 4 for float32");
+    if (rc != 0) return noalloc_fail(rc, err, err_len, "kernel launch failed");
+    return 0;
+}
