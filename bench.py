@@ -32,6 +32,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+PROFILE_RANGE = None         # "decode" / "prefill": bracket that timed region with cudaProfilerStart/Stop
 PUBLISHED_DECODE_B1 = 97.0   # tok/s, batch 1, the reference's README (other hardware)
 
 MODEL = dict(architectures=["Qwen2ForCausalLM"], vocab_size=151936, hidden_size=1536, num_hidden_layers=28,
@@ -182,11 +183,15 @@ def decode_phase(llm, batch, context, steps, warmup, seed):
     torch.cuda.synchronize()
     before = ops.launches
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if PROFILE_RANGE == "decode":
+        torch.cuda.profiler.start()
     t0.record()
     for i in range(warmup, warmup + steps):
         runner.step([StepItem(s, [toks[i][j]], (0,)) for j, s in enumerate(slots)])
     t1.record()
     torch.cuda.synchronize()
+    if PROFILE_RANGE == "decode":
+        torch.cuda.profiler.stop()
     ms = t0.elapsed_time(t1) / steps
     launches = (ops.launches - before) / steps
     for s in slots:
@@ -232,10 +237,14 @@ def prefill_phase(llm, T, reps, seed):
         s = cache.acquire("prefill")
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        if PROFILE_RANGE == "prefill" and i == reps + 2:
+            torch.cuda.profiler.start()
         t0.record()
         runner.step([StepItem(s, ids, (T - 1,))])
         t1.record()
         torch.cuda.synchronize()
+        if PROFILE_RANGE == "prefill" and i == reps + 2:
+            torch.cuda.profiler.stop()
         if i >= 3:
             times.append(t0.elapsed_time(t1))
         cache.release(s)
@@ -268,13 +277,21 @@ def run_ours(args):
     wbytes = weight_bytes(llm.model)
     kvb = kv_bytes_per_token(llm.model, llm.cache)
 
+    T = 2048
+    if args.only == "prefill":
+        pre_ms = prefill_phase(llm, T, reps=2, seed=3)
+        print(json.dumps({"only": "prefill", "tokens": T, "ms": round(pre_ms, 3), "layers": layers}))
+        return 0
     sampler = ClockSampler()
     sampler.start()
     ms, launches = decode_phase(llm, batch, context, args.steps, args.warmup, seed=1)
     clocks = sampler.stop()
+    if args.only == "decode":
+        print(json.dumps({"only": "decode", "batch": batch, "context": context, "ms_per_step": round(ms, 4),
+                          "launches_per_step": launches, "layers": layers}))
+        return 0
 
     e2e_ms = e2e_phase(llm, batch, context, args.steps, args.warmup, seed=2)
-    T = 2048
     pre_ms = prefill_phase(llm, T, reps=5, seed=3)
     points = {}
     if not args.no_points:
@@ -328,6 +345,10 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one phase only and print a short line (for profiling; not a bench value)")
+    ap.add_argument("--profile-range", choices=["decode", "prefill"], default=None,
+                    help="bracket that phase's timed region with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
@@ -339,6 +360,10 @@ def main():
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (this engine runs on a single GPU)")
         return 2
     args.warmup = max(args.warmup, 3)
+    global PROFILE_RANGE
+    PROFILE_RANGE = args.profile_range
+    if args.only:
+        args.no_points = True
     return run_ours(args)
 
 

@@ -42,7 +42,7 @@ class PagePool:
     def share(self, pages: Iterable[int]) -> None:
         """One more holder for each page (pico_vllm/blockmanager.py:120-124)."""
         for p in pages:
-            if self._refs[p] < 1:
+            if not 0 <= p < self.num_pages or self._refs[p] < 1:
                 raise PicoError(f"page {p} is not held, it cannot be shared")
             self._refs[p] += 1
 

@@ -134,44 +134,44 @@ class Scheduler:
             plan.append(Scheduled(req, req.num_computed, n, req.num_computed + n == req.total_len))
             budget -= n
 
-        # 1. running requests, oldest first: one token for decoding ones, a portion for the others
-        i = 0
-        while i < len(self.running):
-            req = self.running[i]
+        # 1. running requests: one token for each decoding request first, then portions of
+        #    prompts, oldest request first in both passes
+        for req in ([r for r in self.running if r.is_decoding] + [r for r in self.running if not r.is_decoding]):
+            if req.status is not RequestStatus.RUNNING:
+                continue                # pre-empted earlier in this step
             if budget <= 0:
                 break
             n = 1 if req.is_decoding else min(req.remaining, self.chunk, budget)
+            gone = False
             while not fits(req, n):
                 victim = self.running[-1]
                 if victim is req:
                     if len(self.running) == 1 and not plan:
-                        if n > 1 and fits(req, 1):
-                            # a shorter portion still fits: find the longest that does
-                            while n > 1 and not fits(req, n):
-                                n -= 1
+                        # alone and still too big: a shorter portion may fit
+                        while n > 1 and not fits(req, n):
+                            n -= 1
+                        if fits(req, n):
                             break
                         raise OutOfPages(f"request {req.request_id} cannot go on even with the cache to itself "
                                          f"({req.total_len} tokens; {self.cache.num_pages} pages of "
                                          f"{self.cache.page_size})")
                     self._preempt(req)
                     preempted.add(req.request_id)
-                    req = None
+                    gone = True
                     break
                 # the victim may already be in this step's plan: take it out again
-                for k, s in enumerate(plan):
-                    if s.request is victim:
-                        need = self.cache.pages_needed(victim.slot, s.count)
+                for k, sch in enumerate(plan):
+                    if sch.request is victim:
+                        need = self.cache.pages_needed(victim.slot, sch.count)
                         for gi, p in enumerate(need):
                             reserve[gi] -= p
-                        budget += s.count
+                        budget += sch.count
                         del plan[k]
                         break
                 self._preempt(victim)
                 preempted.add(victim.request_id)
-            if req is None:
-                continue        # the list shrank; index i now names the next request (or the end)
-            take(req, n)
-            i += 1
+            if not gone:
+                take(req, n)
 
         # 2. new requests, first come first served, while slots, budget and pages last
         while (self.waiting and budget > 0 and len(self.running) < self.max_num_seqs
