@@ -37,3 +37,9 @@ class Batch:
     attn_splits: int = 1         # parts each token's key range is cut into
     scratch: Optional[torch.Tensor] = None   # float32 scratch for split attention
     decode_only: bool = False
+    # the batch split for kernels that treat portions and single tokens differently
+    prefill_segs: Optional[torch.Tensor] = None   # int32: segments with two or more tokens (None: all)
+    num_prefill_segs: int = 0
+    max_prefill_q: int = 0
+    decode_tokens: Optional[torch.Tensor] = None  # int32: tokens of one-token segments (None: every token)
+    num_decode_tokens: int = 0

@@ -48,6 +48,7 @@ class _Layout:
             return start
         self.token_ids, self.positions, self.tok_seg = take(T), take(T), take(T)
         self.seg_slots, self.cu_q, self.logit_rows = take(S), take(S + 1), take(R)
+        self.prefill_segs, self.decode_tokens = take(S), take(T)
         self.g_slots = [take(T) for _ in range(n_groups)]
         self.g_tables = [take(S * width) for _ in range(n_groups)]
         self.total = off
@@ -218,6 +219,10 @@ class ModelRunner:
             cu[i] = at
             at += 1
         cu[S] = at
+        pf = [i for i, n in enumerate(q_lens) if n > 1]
+        dec = [int(cu[i]) for i, n in enumerate(q_lens) if n == 1] + list(range(T_real, T))
+        h[lay.prefill_segs:lay.prefill_segs + len(pf)] = np.asarray(pf, dtype=np.int32)
+        h[lay.decode_tokens:lay.decode_tokens + len(dec)] = np.asarray(dec, dtype=np.int32)
         rows = h[lay.logit_rows:lay.logit_rows + R]
         rows[:] = 0
         rows[:R_real] = np.asarray(want_rows, dtype=np.int32)
@@ -246,7 +251,11 @@ class ModelRunner:
                      logit_rows=d(lay.logit_rows, R), num_logit_rows=R, groups=groups, q_lens=q_lens,
                      kv_lens=kv_lens, attn_splits=splits,
                      scratch=scratch if scratch is not None else self._scratch_for(T, splits),
-                     decode_only=all(n == 1 for n in q_lens))
+                     decode_only=all(n == 1 for n in q_lens),
+                     prefill_segs=d(lay.prefill_segs, len(pf)) if len(pf) < S else None, num_prefill_segs=len(pf),
+                     max_prefill_q=max([q_lens[i] for i in pf], default=0),
+                     decode_tokens=d(lay.decode_tokens, len(dec)) if len(dec) < T else None,
+                     num_decode_tokens=len(dec))
 
     # ------------------------------------------------------------------ CUDA graph replay of decode steps
     def _bucket(self, n: int) -> int:

@@ -52,6 +52,9 @@ def library():
         "pico_rope_store": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
         "pico_paged_attention_generic": [vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32,
                                          i32, i32, f32, i32, i32, vp],
+        "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
+        "pico_paged_decode_mma": [vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+                                  f32, i32, vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_bf16_to_f32": [vp, vp, i64, vp],
     }
@@ -225,6 +228,65 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         int(window) if window else 0, float(scale), n_splits, _dtype_code(q), _stream()),
         f"paged_attention (head_dim {head_dim})")
     _count(2 if n_splits > 1 else 1)
+    return out
+
+
+def mma_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    """True when the tensor-core attention kernels take these sizes (else use paged_attention)."""
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 16)
+
+
+def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                        tok_seg: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+                        cu_q: torch.Tensor, prefill_segs: Optional[torch.Tensor], n_prefill_segs: int,
+                        max_prefill_q: int, decode_tokens: Optional[torch.Tensor], n_decode_tokens: int,
+                        n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
+                        scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same attention as :func:`paged_attention` for bfloat16 on tensor cores, in two launches:
+    segments that bring two or more tokens (``prefill_segs`` int32 [n_prefill_segs], None = all
+    segments; ``cu_q`` int32 [segments + 1]; ``max_prefill_q`` their longest) and single tokens
+    (``decode_tokens`` int32 [n_decode_tokens], None = every token of the batch) whose key range is
+    cut into ``n_splits`` parts.  Every token of the batch must be in exactly one of the two."""
+    _cuda(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs, decode_tokens, scratch)
+    T = q.shape[0]
+    if not mma_attention_takes(q.dtype, n_heads, n_kv_heads, head_dim):
+        raise KernelError(f"paged_attention_mma: bfloat16, head_dim multiple of 16 up to 256 and at most 16 query "
+                          f"heads per kv head (got {q.dtype}, {head_dim}, {n_heads}/{n_kv_heads})")
+    if q.stride(1) != 1 or q.shape[1] < n_heads * head_dim or out.shape != (T, n_heads * head_dim):
+        raise KernelError("paged_attention_mma: bad q or out shape")
+    if not (out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.stride(1) == 1):
+        raise KernelError("paged_attention_mma: out, pages and block_table rows must be contiguous")
+    if tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError("paged_attention_mma: pages must be [pages, kv_heads, page_size, head_dim]")
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
+        raise KernelError("paged_attention_mma: q, pages and out must share one dtype")
+    for t in (tok_seg, positions, block_table, cu_q, prefill_segs, decode_tokens):
+        if t is not None and t.dtype != torch.int32:
+            raise KernelError("paged_attention_mma: index tensors must be int32")
+    lib = library()
+    win = int(window) if window else 0
+    if n_prefill_segs > 0:
+        _check(lib.pico_paged_prefill_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out),
+                                          _ptr(prefill_segs), n_prefill_segs, _ptr(cu_q), max_prefill_q,
+                                          _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
+                                          n_kv_heads, head_dim, page_size, win, float(scale), _stream()),
+               f"paged_prefill_mma (head_dim {head_dim})")
+        _count()
+    if n_decode_tokens > 0:
+        part_o = part_ml = None
+        if n_splits > 1:
+            need = attention_scratch_floats(T, n_heads, head_dim, n_splits)
+            if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+                raise KernelError(f"paged_attention_mma: n_splits={n_splits} needs {need} float32 of scratch")
+            part_o = scratch.data_ptr()
+            part_ml = part_o + 4 * T * n_heads * n_splits * head_dim
+        _check(lib.pico_paged_decode_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o,
+                                         part_ml, _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg),
+                                         _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
+                                         n_kv_heads, head_dim, page_size, win, float(scale), n_splits, _stream()),
+               f"paged_decode_mma (head_dim {head_dim})")
+        _count(2 if n_splits > 1 else 1)
     return out
 
 

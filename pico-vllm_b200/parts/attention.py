@@ -50,7 +50,14 @@ class GQAAttention(Part):
                        gb.slots if cache.store else None, cache.k, cache.v,
                        self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size)
         out = torch.empty((h.shape[0], self.n_heads * self.head_dim), dtype=h.dtype, device=h.device)
-        ops.paged_attention(qkv, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
-                            self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size, self.window,
-                            self.scale, batch.attn_splits, batch.scratch)
+        if ops.mma_attention_takes(h.dtype, self.n_heads, self.n_kv_heads, self.head_dim):
+            ops.paged_attention_mma(qkv, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
+                                    batch.cu_q, batch.prefill_segs, batch.num_prefill_segs, batch.max_prefill_q,
+                                    batch.decode_tokens, batch.num_decode_tokens, self.n_heads, self.n_kv_heads,
+                                    self.head_dim, cache.page_size, self.window, self.scale, batch.attn_splits,
+                                    batch.scratch)
+        else:       # float32, or sizes the tensor-core kernels do not take
+            ops.paged_attention(qkv, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
+                                self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size, self.window,
+                                self.scale, batch.attn_splits, batch.scratch)
         return ops.linear(out, self.o_weight)

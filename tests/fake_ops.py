@@ -94,6 +94,18 @@ def paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n
     return out
 
 
+def mma_attention_takes(dtype, n_heads, n_kv_heads, head_dim):
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 16)
+
+
+def paged_attention_mma(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs,
+                        n_prefill_segs, max_prefill_q, decode_tokens, n_decode_tokens, n_heads, n_kv_heads, head_dim,
+                        page_size, window, scale, n_splits=1, scratch=None):
+    return paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads, head_dim,
+                           page_size, window, scale)
+
+
 def linear(x, weight, out=None):
     y = (x.float() @ weight.float().t()).to(x.dtype)
     if out is not None:
@@ -125,6 +137,7 @@ def sample(logits, temperature, top_p, uniform, out):
 
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
+         "mma_attention_takes", "paged_attention_mma",
          "linear", "logits_linear", "sample"]
 
 

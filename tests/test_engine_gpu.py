@@ -190,7 +190,9 @@ def test_parts_alone(dtype):
     pos = torch.arange(T, dtype=torch.int32, device=DEV)
     slots = (table[0].long()[pos.long() // ps] * ps + pos.long() % ps).to(torch.int32)
     zero = torch.zeros(T, dtype=torch.int32, device=DEV)
-    batch = Batch(T, 1, zero, pos, zero, zero[:1], zero[:2], zero[:0], 0, {0: GroupBatch(slots, table)}, [T], [T])
+    cu = torch.tensor([0, T], dtype=torch.int32, device=DEV)
+    batch = Batch(T, 1, zero, pos, zero, zero[:1], cu, zero[:0], 0, {0: GroupBatch(slots, table)}, [T], [T],
+                  num_prefill_segs=1, max_prefill_q=T)
     got = attn.forward(h.to(DEV), batch, CacheView(group=0, k=pages[0], v=pages[1], page_size=ps)).cpu().float()
     pw = {f"{n}_proj.weight": ws[n].to(dtype).float() for n in "qkv"}
     pw.update({f"{n}_proj.bias": bs[n] for n in "qkv"})

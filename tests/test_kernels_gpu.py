@@ -98,7 +98,7 @@ def test_rope_store(dtype, nh, nkv, hd, ps, rot):
     assert torch.allclose(qg2.cpu().float()[:, :nh * hd], qr.float()[:, :nh * hd], **t)
 
 
-def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, seed=0, spike=False):
+def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, seed=0, spike=False, mma=False):
     """Segments with kv lengths seg_lens, of which the last q_lens are this step's queries."""
     from pico_vllm_b200 import ops
     g = gen(20 + seed)
@@ -133,8 +133,17 @@ def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, se
     if splits > 1:
         scratch = torch.empty(ops.attention_scratch_floats(T, nh, hd, splits), dtype=torch.float32, device=DEV)
     scale = 1.0 / math.sqrt(hd)
-    ops.paged_attention(q.to(DEV), k.to(DEV), v.to(DEV), out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
-                        nh, nkv, hd, ps, window, scale, splits, scratch)
+    if mma:
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+        pf = torch.tensor([i for i, n in enumerate(q_lens) if n > 1], dtype=torch.int32)
+        dec = torch.tensor([int(cu[i]) for i, n in enumerate(q_lens) if n == 1], dtype=torch.int32)
+        out.fill_(float("nan"))
+        ops.paged_attention_mma(q.to(DEV), k.to(DEV), v.to(DEV), out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
+                                cu.to(DEV), pf.to(DEV), len(pf), max([n for n in q_lens if n > 1], default=0),
+                                dec.to(DEV), len(dec), nh, nkv, hd, ps, window, scale, splits, scratch)
+    else:
+        ops.paged_attention(q.to(DEV), k.to(DEV), v.to(DEV), out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
+                            nh, nkv, hd, ps, window, scale, splits, scratch)
     want = torch.empty(T, nh * hd, dtype=dtype)
     fake_ops.paged_attention(q, k, v, want, tok_seg, pos, table, nh, nkv, hd, ps, window, scale)
     return out.cpu().float(), want.float()
@@ -166,6 +175,38 @@ def test_paged_attention_far_key_and_window_edge(dtype, window, splits):
     got, want = _attention_case(dtype, 4, 2, 32, 8, window, seg_lens=[517, 300], q_lens=[1, 2], splits=splits,
                                 seed=5, spike=True)
     assert torch.allclose(got, want, **tol(dtype))
+
+
+MMA_TOL = dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 16, 16), (6, 3, 32, 8), (5, 1, 48, 4), (12, 2, 128, 16), (3, 3, 80, 16),
+                                          (8, 1, 256, 32), (28, 4, 128, 16), (16, 1, 64, 16), (4, 4, 112, 2)])
+@pytest.mark.parametrize("window", [None, 24, 200])
+def test_mma_attention_mixed_segments(nh, nkv, hd, ps, window):
+    # long portions (several 64-row tiles), short ones, single tokens with long and short contexts
+    got, want = _attention_case(torch.bfloat16, nh, nkv, hd, ps, window, seg_lens=[300, 133, 9, 1, 70, 2, 64],
+                                q_lens=[257, 1, 2, 1, 33, 2, 1], splits=1, mma=True)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 64), (12, 2, 128), (7, 1, 96)])
+def test_mma_decode_split_keys(splits, window, nh, nkv, hd):
+    got, want = _attention_case(torch.bfloat16, nh, nkv, hd, 16, window, seg_lens=[700, 333, 40, 3, 64, 65, 1],
+                                q_lens=[1, 1, 1, 1, 1, 1, 1], splits=splits, seed=3, mma=True)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("window,splits,q_lens", [(None, 1, [1, 2]), (None, 8, [1, 1]), (64, 1, [1, 2]), (64, 4, [1, 1]),
+                                                  (None, 1, [200, 150]), (64, 1, [200, 150])])
+def test_mma_attention_far_key_and_window_edge(window, splits, q_lens):
+    got, want = _attention_case(torch.bfloat16, 4, 2, 32, 8, window, seg_lens=[517, 300], q_lens=q_lens, splits=splits,
+                                seed=5, spike=True, mma=True)
+    assert torch.allclose(got, want, **MMA_TOL)
 
 
 def test_refuses_head_sizes_it_does_not_take():
