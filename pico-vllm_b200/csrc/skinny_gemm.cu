@@ -1,0 +1,313 @@
+// Matrix products for a handful of tokens (decode): y[m, n] = sum_k x[m, k] w[n, k], bfloat16 in,
+// float32 accumulate, for M <= 16 tokens.  At this size the product is a stream of the weight
+// matrix from HBM, so the kernel is built around that stream: one block owns 16 output features
+// for ALL tokens over the WHOLE of K (no split-K, hence no second pass and a fixed summation
+// order), its 4 warps take alternate 64-wide slices of K, weights and activations come in through
+// a 6-stage cp.async pipeline (8 KB of weights per stage), the products run on tensor cores with
+// the weights as the 16-row operand (mma.sync m16n8k16: rows = output features, columns = tokens),
+// and the four warps' sums are added in shared memory.  The 16 features of a block are two runs of
+// 8 consecutive rows of w, which lets the epilogue see pairs that belong together:
+//
+//   STORE     y = (sum + bias) as bfloat16 or float32                       (plain projection, head)
+//   RESIDUAL  x_res[m, n] += sum, float32 in place                          (o_proj, down_proj)
+//   SWIGLU    a[m, i] = silu(gate_i) * up_i; rows i (gate) and I + i (up)   (gate_up, no 2I buffer)
+//   ROPE      q/k heads: rows d and d + hd/2 of a head: bias, rotation by the token's position,
+//             q to the query buffer, k and v straight into their cache pages   (qkv projection)
+//
+// The reference runs these as cuBLAS nn.Linear calls followed by separate kernels
+// (pico_vllm/model.py:200-225, 290-295, 326-332; pico_vllm/kernels/swiglu.py,
+// pico_vllm/kernels/fused_rope_kvcache_store.py); the formulas are the same: silu(g) = g * sigmoid(g)
+// (swiglu.py:36-41), x1' = x1 c - x2 s, x2' = x2 c + x1 s with angle = position * theta^(-2i/hd)
+// (fused_rope_kvcache_store.py:60-65; model.py:80-86), cache row = page * page_size + offset
+// (store_kvcache.py:24-50).
+#include "common.cuh"
+
+#define SG_THREADS 128
+#define SG_KB 256              // K per pipeline stage (64 per warp)
+#define SG_STAGES 6
+#define SG_LD (SG_KB + 8)      // padded row of a stage in shared memory (elements)
+
+enum { SG_STORE = 0, SG_RESIDUAL = 1, SG_SWIGLU = 2, SG_ROPE = 3 };
+
+struct SkinnyArgs {
+    const bf16* w;            // [N, K]
+    const bf16* x;            // [M, K] (row stride ldx)
+    int ldx;
+    int M, N, K;
+    // STORE
+    void* out;                // [M, ld_out] bf16 or float32
+    int ld_out;
+    int out_f32;
+    const float* bias;        // [N] or null (STORE and ROPE)
+    // RESIDUAL
+    float* resid;             // [M, N]
+    // SWIGLU: N = 2 * I; out = [M, I] bf16 in `out`
+    // ROPE
+    int nh, nkv, hd, rot_half, page_size;
+    const int* positions;     // [M]
+    const int* slots;         // [M] or null
+    const float* inv_freq;    // [rot_half]
+    bf16* q_out;              // [M, nh * hd]
+    bf16* k_pages;
+    bf16* v_pages;
+};
+
+__device__ __forceinline__ uint32_t sg_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void sg_cp16(uint32_t dst, const void* src, bool pred) {
+    const int n = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void sg_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void sg_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void sg_ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sg_ldmatrix_x2(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void sg_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The two runs of 8 weight rows a block owns.
+template <int EPI>
+__device__ __forceinline__ void sg_rows(const SkinnyArgs& p, int tile, int& row_a, int& row_b) {
+    if (EPI == SG_SWIGLU) {
+        row_a = tile * 8;                  // gate rows
+        row_b = p.N / 2 + tile * 8;        // the same features' up rows
+    } else if (EPI == SG_ROPE) {
+        const int per_head = p.hd / 16;    // tiles per head
+        const int rot_heads = p.nh + p.nkv;
+        const int head = tile / per_head, j = tile - head * per_head;
+        if (head < rot_heads) {            // q or k head: dims 8j.. and hd/2 + 8j..
+            row_a = head * p.hd + j * 8;
+            row_b = row_a + p.hd / 2;
+        } else {                           // v head: 16 consecutive dims
+            row_a = head * p.hd + j * 16;
+            row_b = row_a + 8;
+        }
+    } else {
+        row_a = tile * 16;
+        row_b = row_a + 8;
+    }
+}
+
+template <int MT, int EPI>     // MT: tokens padded to 8 * MT
+__global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArgs p) {
+    extern __shared__ __align__(16) unsigned char sg_smem[];
+    constexpr int XR = MT * 8;                       // token rows of a stage
+    constexpr int STAGE_ELEMS = (16 + XR) * SG_LD;
+    bf16* stages = reinterpret_cast<bf16*>(sg_smem);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int row_a, row_b;
+    sg_rows<EPI>(p, blockIdx.x, row_a, row_b);
+    const int nk = (p.K + SG_KB - 1) / SG_KB;
+
+    auto load_stage = [&](int kb, int s) {
+        bf16* ws = stages + s * STAGE_ELEMS;
+        bf16* xs = ws + 16 * SG_LD;
+        const int k0 = kb * SG_KB;
+        // weights: 16 rows x 32 chunks of 16 bytes
+        for (int idx = threadIdx.x; idx < 16 * (SG_KB / 8); idx += SG_THREADS) {
+            const int r = idx / (SG_KB / 8), c = idx - r * (SG_KB / 8);
+            const int k = k0 + c * 8;
+            const int row = (r < 8 ? row_a + r : row_b + r - 8);
+            const bool ok = k < p.K;
+            sg_cp16(sg_smem_u32(ws + r * SG_LD + c * 8), p.w + (size_t)row * p.K + (ok ? k : 0), ok);
+        }
+        for (int idx = threadIdx.x; idx < XR * (SG_KB / 8); idx += SG_THREADS) {
+            const int r = idx / (SG_KB / 8), c = idx - r * (SG_KB / 8);
+            const int k = k0 + c * 8;
+            const bool ok = k < p.K && r < p.M;
+            sg_cp16(sg_smem_u32(xs + r * SG_LD + c * 8), p.x + (size_t)(ok ? r : 0) * p.ldx + (ok ? k : 0), ok);
+        }
+    };
+
+#pragma unroll
+    for (int s = 0; s < SG_STAGES - 1; ++s) {
+        if (s < nk) load_stage(s, s);
+        sg_commit();
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_row = lane & 7, b_col = ((lane >> 3) & 1) * 8;
+    for (int kb = 0; kb < nk; ++kb) {
+        sg_wait<SG_STAGES - 2>();
+        __syncthreads();
+        const int nxt = kb + SG_STAGES - 1;
+        if (nxt < nk) load_stage(nxt, nxt % SG_STAGES);
+        sg_commit();
+        const bf16* ws = stages + (kb % SG_STAGES) * STAGE_ELEMS;
+        const bf16* xs = ws + 16 * SG_LD;
+        const int kw = warp * 64;                    // this warp's slice of the stage
+#pragma unroll
+        for (int ks = 0; ks < 64; ks += 16) {
+            uint32_t a[4];
+            sg_ldmatrix_x4(a, sg_smem_u32(ws + a_row * SG_LD + kw + ks + a_col));
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) {
+                uint32_t b[2];
+                sg_ldmatrix_x2(b, sg_smem_u32(xs + (nt * 8 + b_row) * SG_LD + kw + ks + b_col));
+                sg_mma(acc[nt], a, b[0], b[1]);
+            }
+        }
+    }
+    sg_wait<0>();
+    __syncthreads();
+    // add the four warps' sums: red[warp][feature 0..15][token 0..XR-1]
+    float* red = reinterpret_cast<float*>(sg_smem);
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int f = (lane >> 2) + (e >> 1) * 8;
+            const int t = nt * 8 + (lane & 3) * 2 + (e & 1);
+            red[(warp * 16 + f) * XR + t] = acc[nt][e];
+        }
+    }
+    __syncthreads();
+
+    if (EPI == SG_STORE || EPI == SG_RESIDUAL) {
+        for (int idx = threadIdx.x; idx < 16 * XR; idx += SG_THREADS) {
+            const int t = idx / 16, f = idx - t * 16;          // consecutive threads: consecutive features
+            if (t >= p.M) continue;
+            const float v = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+            const int n = (f < 8 ? row_a + f : row_b + f - 8);
+            if (EPI == SG_RESIDUAL) {
+                p.resid[(size_t)t * p.N + n] += v;
+            } else {
+                const float y = v + (p.bias ? p.bias[n] : 0.f);
+                if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)t * p.ld_out + n] = y;
+                else reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ld_out + n] = __float2bfloat16_rn(y);
+            }
+        }
+    } else if (EPI == SG_SWIGLU) {
+        for (int idx = threadIdx.x; idx < 8 * XR; idx += SG_THREADS) {
+            const int t = idx / 8, f = idx - t * 8;
+            if (t >= p.M) continue;
+            const float gte = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+            const int fu = f + 8;
+            const float up = red[fu * XR + t] + red[(16 + fu) * XR + t] + red[(32 + fu) * XR + t] + red[(48 + fu) * XR + t];
+            const float sl = gte / (1.0f + expf(-gte));
+            reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ld_out + row_a + f] = __float2bfloat16_rn(sl * up);
+        }
+    } else {    // SG_ROPE
+        const int rot_heads = p.nh + p.nkv;
+        const int head = row_a / p.hd;
+        if (head < rot_heads) {
+            const int d0 = row_a - head * p.hd;                 // first dim of the lower half (8j)
+            for (int idx = threadIdx.x; idx < 8 * XR; idx += SG_THREADS) {
+                const int t = idx / 8, f = idx - t * 8;
+                if (t >= p.M) continue;
+                float x1 = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+                const int fu = f + 8;
+                float x2 = red[fu * XR + t] + red[(16 + fu) * XR + t] + red[(32 + fu) * XR + t] + red[(48 + fu) * XR + t];
+                if (p.bias) { x1 += p.bias[row_a + f]; x2 += p.bias[row_b + f]; }
+                float y1 = x1, y2 = x2;
+                const int i = d0 + f;                           // pair index
+                if (i < p.rot_half) {
+                    float s, c;
+                    sincosf((float)p.positions[t] * p.inv_freq[i], &s, &c);
+                    y1 = x1 * c - x2 * s;
+                    y2 = x2 * c + x1 * s;
+                }
+                if (head < p.nh) {
+                    bf16* dst = p.q_out + (size_t)t * p.nh * p.hd + row_a + f;
+                    dst[0] = __float2bfloat16_rn(y1);
+                    dst[p.hd / 2] = __float2bfloat16_rn(y2);
+                } else if (p.slots && p.slots[t] >= 0) {
+                    const int slot = p.slots[t], kh = head - p.nh;
+                    bf16* dst = p.k_pages + (((size_t)(slot / p.page_size) * p.nkv + kh) * p.page_size + slot % p.page_size) * p.hd + i;
+                    dst[0] = __float2bfloat16_rn(y1);
+                    dst[p.hd / 2] = __float2bfloat16_rn(y2);
+                }
+            }
+        } else {
+            const int kh = head - rot_heads;
+            const int d0 = row_a - head * p.hd;
+            for (int idx = threadIdx.x; idx < 16 * XR; idx += SG_THREADS) {
+                const int t = idx / 16, f = idx - t * 16;
+                if (t >= p.M || !p.slots || p.slots[t] < 0) continue;
+                float v = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+                if (p.bias) v += p.bias[row_a + f];
+                const int slot = p.slots[t];
+                p.v_pages[(((size_t)(slot / p.page_size) * p.nkv + kh) * p.page_size + slot % p.page_size) * p.hd + d0 + f] =
+                    __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+static size_t sg_smem_bytes(int mt) { return (size_t)SG_STAGES * (16 + mt * 8) * SG_LD * sizeof(bf16); }
+
+template <int EPI>
+static int sg_launch(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
+    const int mt = (a.M + 7) / 8;
+    const size_t smem = sg_smem_bytes(mt);
+    if (mt == 1) {
+        cudaFuncSetAttribute(skinny_gemm_kernel<1, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        skinny_gemm_kernel<1, EPI><<<tiles, SG_THREADS, smem, stream>>>(a);
+    } else if (mt == 2) {
+        cudaFuncSetAttribute(skinny_gemm_kernel<2, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        skinny_gemm_kernel<2, EPI><<<tiles, SG_THREADS, smem, stream>>>(a);
+    } else
+        return PICO_ERR_SIZE;
+    return pico_launch_status();
+}
+
+static int sg_check(int M, int N, int K, int ldx) {
+    if (M < 1 || M > 16 || K < 16 || K % 16 != 0 || N < 16 || ldx % 8 != 0) return PICO_ERR_SIZE;
+    return 0;
+}
+
+// y = x w^T (+ bias): out [M, ld_out] bfloat16 (out_f32 = 0) or float32 (1).  N % 16 == 0.
+PICO_API int pico_skinny_linear(const void* x, int ldx, const void* w, const float* bias, void* out, int ld_out,
+                                int out_f32, int M, int N, int K, cudaStream_t stream) {
+    if (sg_check(M, N, K, ldx) || N % 16 != 0) return PICO_ERR_SIZE;
+    SkinnyArgs a = {};
+    a.w = (const bf16*)w; a.x = (const bf16*)x; a.ldx = ldx; a.M = M; a.N = N; a.K = K;
+    a.out = out; a.ld_out = ld_out; a.out_f32 = out_f32; a.bias = bias;
+    return sg_launch<SG_STORE>(a, N / 16, stream);
+}
+
+// resid[M, N] (float32) += x w^T.  N % 16 == 0.
+PICO_API int pico_skinny_linear_residual(const void* x, int ldx, const void* w, float* resid, int M, int N, int K,
+                                         cudaStream_t stream) {
+    if (sg_check(M, N, K, ldx) || N % 16 != 0) return PICO_ERR_SIZE;
+    SkinnyArgs a = {};
+    a.w = (const bf16*)w; a.x = (const bf16*)x; a.ldx = ldx; a.M = M; a.N = N; a.K = K; a.resid = resid;
+    return sg_launch<SG_RESIDUAL>(a, N / 16, stream);
+}
+
+// out[M, I] = silu(x wg^T) * (x wu^T) with w = [wg; wu] of shape [2I, K].  I % 8 == 0.
+PICO_API int pico_skinny_gate_up_swiglu(const void* x, int ldx, const void* w, void* out, int M, int I, int K,
+                                        cudaStream_t stream) {
+    if (sg_check(M, 2 * I, K, ldx) || I % 8 != 0) return PICO_ERR_SIZE;
+    SkinnyArgs a = {};
+    a.w = (const bf16*)w; a.x = (const bf16*)x; a.ldx = ldx; a.M = M; a.N = 2 * I; a.K = K;
+    a.out = out; a.ld_out = I;
+    return sg_launch<SG_SWIGLU>(a, I / 8, stream);
+}
+
+// qkv projection with bias, rotary encoding and cache store fused: q_out [M, nh*hd] gets the rotated
+// queries, rotated keys and the values go to their cache rows (slots[m], -1 or null = no store).
+// w: [(nh + 2 nkv) * hd, K], rows ordered q heads, k heads, v heads.  hd % 16 == 0.
+PICO_API int pico_skinny_qkv_rope_store(const void* x, int ldx, const void* w, const float* bias, void* q_out,
+                                        const int* positions, const float* inv_freq, int rot_dim, const int* slots,
+                                        void* k_pages, void* v_pages, int M, int K, int nh, int nkv, int hd,
+                                        int page_size, cudaStream_t stream) {
+    const int N = (nh + 2 * nkv) * hd;
+    if (sg_check(M, N, K, ldx) || hd % 16 != 0 || rot_dim % 2 != 0 || rot_dim > hd) return PICO_ERR_SIZE;
+    SkinnyArgs a = {};
+    a.w = (const bf16*)w; a.x = (const bf16*)x; a.ldx = ldx; a.M = M; a.N = N; a.K = K; a.bias = bias;
+    a.nh = nh; a.nkv = nkv; a.hd = hd; a.rot_half = rot_dim / 2; a.page_size = page_size;
+    a.positions = positions; a.slots = slots; a.inv_freq = inv_freq;
+    a.q_out = (bf16*)q_out; a.k_pages = (bf16*)k_pages; a.v_pages = (bf16*)v_pages;
+    return sg_launch<SG_ROPE>(a, N / 16, stream);
+}

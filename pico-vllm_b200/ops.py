@@ -55,6 +55,10 @@ def library():
         "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
         "pico_paged_decode_mma": [vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                                   f32, i32, vp],
+        "pico_skinny_linear": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+        "pico_skinny_linear_residual": [vp, i32, vp, vp, i32, i32, i32, vp],
+        "pico_skinny_gate_up_swiglu": [vp, i32, vp, vp, i32, i32, i32, vp],
+        "pico_skinny_qkv_rope_store": [vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_bf16_to_f32": [vp, vp, i64, vp],
     }
@@ -290,6 +294,92 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     return out
 
 
+# ------------------------------------------------------------------------------------------
+# Products for a handful of tokens (decode): own kernels that stream the weights once and fuse
+# what follows the product.  ``skinny_takes`` says whether the sizes fit; callers fall back to
+# ``linear`` + the separate kernels otherwise.
+SKINNY_MAX_TOKENS = 16
+
+
+def skinny_takes(x: torch.Tensor, weight: torch.Tensor, n_multiple: int = 16) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and 1 <= x.shape[0] <= SKINNY_MAX_TOKENS and x.shape[1] % 16 == 0 and x.shape[1] >= 16
+            and weight.shape[0] % n_multiple == 0 and weight.shape[0] >= 16
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous())
+
+
+def skinny_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """x [M<=16, K] times weight[N, K] transposed (+ bias), bfloat16 in, out bfloat16 or float32."""
+    _cuda(x, weight, bias)
+    if not skinny_takes(x, weight):
+        raise KernelError("skinny_linear: needs bfloat16, at most 16 tokens, K and N multiples of 16")
+    M, K = x.shape
+    N = weight.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(library().pico_skinny_linear(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(out), N,
+                                        1 if out_dtype == torch.float32 else 0, M, N, K, _stream()), "skinny_linear")
+    _count()
+    return out
+
+
+def skinny_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual [M, N] float32 += x [M<=16, K] times weight[N, K] transposed, in one kernel."""
+    _cuda(x, weight, residual)
+    M, K = x.shape
+    N = weight.shape[0]
+    if not skinny_takes(x, weight) or residual.dtype != torch.float32 or residual.shape != (M, N) \
+            or not residual.is_contiguous():
+        raise KernelError("skinny_linear_residual: needs bfloat16 x and weight, float32 contiguous residual [M, N]")
+    _check(library().pico_skinny_linear_residual(_ptr(x), x.stride(0), _ptr(weight), _ptr(residual), M, N, K,
+                                                 _stream()), "skinny_linear_residual")
+    _count()
+
+
+def skinny_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+    """silu(x wg^T) * (x wu^T) for gate_up_weight = [wg; wu] ([2I, K]); returns [M, I] bfloat16."""
+    _cuda(x, gate_up_weight)
+    if not skinny_takes(x, gate_up_weight):
+        raise KernelError("skinny_gate_up_swiglu: needs bfloat16, at most 16 tokens, K and 2I multiples of 16")
+    M, K = x.shape
+    I = gate_up_weight.shape[0] // 2
+    out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
+    _check(library().pico_skinny_gate_up_swiglu(_ptr(x), x.stride(0), _ptr(gate_up_weight), _ptr(out), M, I, K,
+                                                _stream()), "skinny_gate_up_swiglu")
+    _count()
+    return out
+
+
+def skinny_qkv_rope_store(x: torch.Tensor, qkv_weight: torch.Tensor, bias: Optional[torch.Tensor],
+                          positions: torch.Tensor, inv_freq: torch.Tensor, slots: Optional[torch.Tensor],
+                          k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], n_heads: int,
+                          n_kv_heads: int, head_dim: int, page_size: int) -> torch.Tensor:
+    """qkv projection, bias, rotary encoding and cache store in one kernel; returns the rotated
+    queries [M, n_heads * head_dim] bfloat16.  Same meaning as ``linear`` + ``rope_store``."""
+    _cuda(x, qkv_weight, bias, positions, inv_freq, slots, k_pages, v_pages)
+    M, K = x.shape
+    if not skinny_takes(x, qkv_weight) or head_dim % 16 != 0 \
+            or qkv_weight.shape[0] != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError("skinny_qkv_rope_store: sizes not taken")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (qkv_weight.shape[0],)):
+        raise KernelError("skinny_qkv_rope_store: bias must be float32 of the qkv width")
+    if positions.dtype != torch.int32 or inv_freq.dtype != torch.float32:
+        raise KernelError("skinny_qkv_rope_store: positions int32, inv_freq float32")
+    if slots is not None:
+        if slots.dtype != torch.int32 or k_pages is None or v_pages is None:
+            raise KernelError("skinny_qkv_rope_store: slots must be int32 and come with pages")
+        for pg in (k_pages, v_pages):
+            if pg.dtype != torch.bfloat16 or not pg.is_contiguous() or tuple(pg.shape[1:]) != (n_kv_heads, page_size, head_dim):
+                raise KernelError("skinny_qkv_rope_store: pages must be contiguous bfloat16 [pages, kv_heads, page_size, head_dim]")
+    q = torch.empty((M, n_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    _check(library().pico_skinny_qkv_rope_store(_ptr(x), x.stride(0), _ptr(qkv_weight), _ptr(bias), _ptr(q),
+                                                _ptr(positions), _ptr(inv_freq), 2 * inv_freq.shape[0], _ptr(slots),
+                                                _ptr(k_pages), _ptr(v_pages), M, K, n_heads, n_kv_heads, head_dim,
+                                                page_size, _stream()), "skinny_qkv_rope_store")
+    _count()
+    return q
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [T, K] times weight[N, K] transposed, a library matrix product (cuBLAS through torch).
 
@@ -315,6 +405,8 @@ def logits_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     _cuda(x, weight)
     if x.dtype == torch.float32 and weight.dtype == torch.float32:
         return torch.mm(x, weight.t())
+    if skinny_takes(x, weight):
+        return skinny_linear(x, weight, None, torch.float32)
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     if x.dtype == torch.bfloat16 and weight.dtype == torch.float32:

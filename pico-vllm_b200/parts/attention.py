@@ -20,6 +20,8 @@ from .registry import register
 
 @register("mixer", "gqa_attention")
 class GQAAttention(Part):
+    fuses_residual = True   # forward(..., residual=x) may add its output to x and return None
+
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, position: Part,
                  qkv_bias: bool = True, window: Optional[int] = None, scale: Optional[float] = None):
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
@@ -43,12 +45,20 @@ class GQAAttention(Part):
     def materialize(self, device, dtype):
         self.position.materialize(device, dtype)
 
-    def forward(self, h: torch.Tensor, batch, cache: CacheView) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, batch, cache: CacheView, residual: Optional[torch.Tensor] = None):
+        """Returns what is to be added to the residual stream - or, when ``residual`` is given
+        and the fused small-batch kernels take the sizes, adds it there itself and returns None."""
         gb = batch.groups[cache.group]
-        qkv = ops.linear(h, self.qkv_weight)
-        ops.rope_store(qkv, self.qkv_bias, batch.positions, self.position.inv_freq,
-                       gb.slots if cache.store else None, cache.k, cache.v,
-                       self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size)
+        slots = gb.slots if cache.store else None
+        if ops.skinny_takes(h, self.qkv_weight):
+            # a handful of tokens: projection, bias, rotation and cache store are one kernel
+            qkv = ops.skinny_qkv_rope_store(h, self.qkv_weight, self.qkv_bias, batch.positions,
+                                            self.position.inv_freq, slots, cache.k, cache.v, self.n_heads,
+                                            self.n_kv_heads, self.head_dim, cache.page_size)
+        else:
+            qkv = ops.linear(h, self.qkv_weight)
+            ops.rope_store(qkv, self.qkv_bias, batch.positions, self.position.inv_freq, slots, cache.k, cache.v,
+                           self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size)
         out = torch.empty((h.shape[0], self.n_heads * self.head_dim), dtype=h.dtype, device=h.device)
         if ops.mma_attention_takes(h.dtype, self.n_heads, self.n_kv_heads, self.head_dim):
             ops.paged_attention_mma(qkv, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
@@ -60,4 +70,7 @@ class GQAAttention(Part):
             ops.paged_attention(qkv, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
                                 self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size, self.window,
                                 self.scale, batch.attn_splits, batch.scratch)
+        if residual is not None and ops.skinny_takes(out, self.o_weight):
+            ops.skinny_linear_residual(out, self.o_weight, residual)
+            return None
         return ops.linear(out, self.o_weight)

@@ -25,6 +25,13 @@ class PreNormBlock:
         """x: float32 residual stream [T, width]; pending: output of the previous part that is
         still to be added to x (or None).  Returns (x, pending) in the same sense."""
         h = self.norm1.add_norm(x, pending)
-        a = self.mixer.forward(h, batch, cache)
+        a = self._call(self.mixer, x, h, batch, cache)
         h = self.norm2.add_norm(x, a)
-        return x, self.feed_forward.forward(h, batch)
+        return x, self._call(self.feed_forward, x, h, batch)
+
+    @staticmethod
+    def _call(part, x, *args):
+        # a part that says ``fuses_residual`` may add its output to x itself and return None
+        if getattr(part, "fuses_residual", False):
+            return part.forward(*args, residual=x)
+        return part.forward(*args)

@@ -5,7 +5,7 @@ the activation runs in float32 as in pico_vllm/kernels/swiglu.py:28-44.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -17,6 +17,8 @@ from .registry import register
 
 @register("feed_forward", "gated_mlp")
 class GatedMLP(Part):
+    fuses_residual = True   # forward(..., residual=x) may add its output to x and return None
+
     def __init__(self, width: int, inner: int, act: str = "silu"):
         if act != "silu":
             raise ConfigError(f"gated_mlp: activation {act!r} is not built (only 'silu')")
@@ -28,8 +30,16 @@ class GatedMLP(Part):
                                          Piece("up.weight", (self.inner, self.width)))),
                 Param("down_weight", (Piece("down.weight", (self.width, self.inner)),))]
 
-    def forward(self, h: torch.Tensor, batch) -> torch.Tensor:
-        gu = ops.linear(h, self.gate_up_weight)
-        a = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
-        ops.swiglu(gu, a)
+    def forward(self, h: torch.Tensor, batch, residual: Optional[torch.Tensor] = None):
+        """Returns what is to be added to the residual stream - or, when ``residual`` is given
+        and the fused small-batch kernels take the sizes, adds it there itself and returns None."""
+        if ops.skinny_takes(h, self.gate_up_weight) and self.inner % 8 == 0:
+            a = ops.skinny_gate_up_swiglu(h, self.gate_up_weight)      # product and activation in one kernel
+        else:
+            gu = ops.linear(h, self.gate_up_weight)
+            a = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+            ops.swiglu(gu, a)
+        if residual is not None and ops.skinny_takes(a, self.down_weight):
+            ops.skinny_linear_residual(a, self.down_weight, residual)
+            return None
         return ops.linear(a, self.down_weight)

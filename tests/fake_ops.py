@@ -106,6 +106,39 @@ def paged_attention_mma(q, k_pages, v_pages, out, tok_seg, positions, block_tabl
                            page_size, window, scale)
 
 
+SKINNY_MAX_TOKENS = 16
+
+
+def skinny_takes(x, weight, n_multiple=16):
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 1 <= x.shape[0] <= 16
+            and x.shape[1] % 16 == 0 and weight.shape[0] % n_multiple == 0 and weight.shape[0] >= 16)
+
+
+def skinny_linear(x, weight, bias=None, out_dtype=torch.bfloat16):
+    y = x.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias
+    return y.to(out_dtype)
+
+
+def skinny_linear_residual(x, weight, residual):
+    residual.add_(x.float() @ weight.float().t())
+
+
+def skinny_gate_up_swiglu(x, gate_up_weight):
+    gu = x.float() @ gate_up_weight.float().t()
+    I = gu.shape[1] // 2
+    g, u = gu[:, :I], gu[:, I:]
+    return (g * torch.sigmoid(g) * u).to(torch.bfloat16)
+
+
+def skinny_qkv_rope_store(x, qkv_weight, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads,
+                          head_dim, page_size):
+    qkv = x.float() @ qkv_weight.float().t()          # float32 until after the rotation, like the kernel
+    rope_store(qkv, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads, head_dim, page_size)
+    return qkv[:, :n_heads * head_dim].to(torch.bfloat16)
+
+
 def linear(x, weight, out=None):
     y = (x.float() @ weight.float().t()).to(x.dtype)
     if out is not None:
@@ -137,7 +170,8 @@ def sample(logits, temperature, top_p, uniform, out):
 
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
-         "mma_attention_takes", "paged_attention_mma",
+         "mma_attention_takes", "paged_attention_mma", "skinny_takes", "skinny_linear", "skinny_linear_residual",
+         "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
          "linear", "logits_linear", "sample"]
 
 

@@ -209,6 +209,69 @@ def test_mma_attention_far_key_and_window_edge(window, splits, q_lens):
     assert torch.allclose(got, want, **MMA_TOL)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(64, 64), (176, 80), (2048, 1536), (1536, 8960), (512, 272)])
+def test_skinny_linear_store_and_residual(M, N, K):
+    from pico_vllm_b200 import ops
+    x = torch.randn(M, K, generator=gen(60)).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=gen(61)) / math.sqrt(K)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=gen(62))
+    want = x.float() @ w.float().t()
+    got = ops.skinny_linear(x.to(DEV), w.to(DEV), bias.to(DEV), torch.float32).cpu()
+    assert torch.allclose(got, want + bias, atol=2e-3, rtol=2e-3)
+    got16 = ops.skinny_linear(x.to(DEV), w.to(DEV)).cpu()
+    assert got16.dtype == torch.bfloat16 and torch.allclose(got16.float(), want, atol=2e-2, rtol=2e-2)
+    res = torch.randn(M, N, generator=gen(63))
+    rg = res.to(DEV)
+    ops.skinny_linear_residual(x.to(DEV), w.to(DEV), rg)
+    assert torch.allclose(rg.cpu(), res + want, atol=2e-3, rtol=2e-3)
+    assert torch.allclose(ops.logits_linear(x.to(DEV), w.to(DEV)).cpu(), want, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,K", [(128, 64), (176, 80), (8960, 1536), (320, 192)])
+def test_skinny_gate_up_swiglu(M, I, K):
+    from pico_vllm_b200 import ops
+    x = torch.randn(M, K, generator=gen(64)).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, generator=gen(65)) * 2 / math.sqrt(K)).to(torch.bfloat16)
+    got = ops.skinny_gate_up_swiglu(x.to(DEV), w.to(DEV)).cpu().float()
+    want = fake_ops.skinny_gate_up_swiglu(x, w).float()
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 8, 16])
+@pytest.mark.parametrize("nh,nkv,hd,ps,rot,K", [(4, 2, 16, 16, 16, 64), (6, 3, 32, 8, 32, 192), (5, 1, 48, 4, 48, 80),
+                                                (12, 2, 128, 16, 128, 1536), (3, 3, 80, 16, 40, 96), (2, 1, 128, 32, 0, 64)])
+def test_skinny_qkv_rope_store(M, nh, nkv, hd, ps, rot, K):
+    from pico_vllm_b200 import ops
+    pages = 12
+    N = (nh + 2 * nkv) * hd
+    x = torch.randn(M, K, generator=gen(66)).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=gen(67)) / math.sqrt(K)).to(torch.bfloat16)
+    bias = 0.5 * torch.randn(N, generator=gen(68))
+    pos = torch.randint(0, 5000, (M,), generator=gen(69), dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2).float() / max(rot, 1))) if rot else torch.zeros(0)
+    slots = torch.randperm(pages * ps, generator=gen(70))[:M].to(torch.int32)
+    if M > 2:
+        slots[1] = -1
+    k0 = torch.randn(pages, nkv, ps, hd, generator=gen(71)).to(torch.bfloat16)
+    v0 = torch.randn(pages, nkv, ps, hd, generator=gen(72)).to(torch.bfloat16)
+    kg, vg = k0.to(DEV), v0.to(DEV)
+    qg = ops.skinny_qkv_rope_store(x.to(DEV), w.to(DEV), bias.to(DEV), pos.to(DEV), inv.to(DEV), slots.to(DEV), kg, vg,
+                                   nh, nkv, hd, ps)
+    kr, vr = k0.clone(), v0.clone()
+    qr = fake_ops.skinny_qkv_rope_store(x, w, bias, pos, inv, slots, kr, vr, nh, nkv, hd, ps)
+    t = dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(qg.cpu().float(), qr.float(), **t)
+    assert torch.allclose(kg.cpu().float(), kr.float(), **t)
+    assert torch.allclose(vg.cpu().float(), vr.float(), **t)
+    # without slots only the queries are produced and the pages stay as they were
+    kg2 = k0.to(DEV)
+    q2 = ops.skinny_qkv_rope_store(x.to(DEV), w.to(DEV), bias.to(DEV), pos.to(DEV), inv.to(DEV), None, None, None,
+                                   nh, nkv, hd, ps)
+    assert torch.allclose(q2.cpu().float(), qr.float(), **t) and torch.equal(kg2.cpu(), k0)
+
+
 def test_refuses_head_sizes_it_does_not_take():
     from pico_vllm_b200 import ops
     from pico_vllm_b200.errors import KernelError
