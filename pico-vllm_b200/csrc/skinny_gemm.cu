@@ -3,10 +3,13 @@
 // matrix from HBM, so the kernel is built around that stream: one block owns 16 output features
 // for ALL tokens over the WHOLE of K (no split-K, hence no second pass and a fixed summation
 // order), its 4 warps take alternate 64-wide slices of K, weights and activations come in through
-// a 6-stage cp.async pipeline (8 KB of weights per stage), the products run on tensor cores with
+// a deep cp.async pipeline (8 KB of weights per stage; 8 stages with two blocks per SM, or 16
+// stages with one block per SM when there are few tiles), the products run on tensor cores with
 // the weights as the 16-row operand (mma.sync m16n8k16: rows = output features, columns = tokens),
-// and the four warps' sums are added in shared memory.  The 16 features of a block are two runs of
-// 8 consecutive rows of w, which lets the epilogue see pairs that belong together:
+// and the four warps' sums are added in shared memory.  Blocks are persistent: a block walks tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ... and its pipeline runs on across tile boundaries, so the
+// weight stream never drains.  The 16 features of a tile are two runs of 8 consecutive rows of w,
+// which lets the epilogue see pairs that belong together:
 //
 //   STORE     y = (sum + bias) as bfloat16 or float32                       (plain projection, head)
 //   RESIDUAL  x_res[m, n] += sum, float32 in place                          (o_proj, down_proj)
@@ -22,10 +25,25 @@
 // (store_kvcache.py:24-50).
 #include "common.cuh"
 
-#define SG_THREADS 128
-#define SG_KB 256              // K per pipeline stage (64 per warp)
-#define SG_STAGES 6
-#define SG_LD (SG_KB + 8)      // padded row of a stage in shared memory (elements)
+#ifndef SG_WARPS
+#define SG_WARPS 8           // warps per block; each takes every SG_WARPS-th 64-wide slice of K
+#endif
+#define SG_THREADS (32 * SG_WARPS)
+#define SG_KW 64               // K per pipeline step of one warp
+#define SG_LD (SG_KW + 8)      // padded row of a stage in shared memory (elements): 144 bytes, conflict-free ldmatrix
+
+#ifndef SG_ST_XPRE
+#define SG_ST_XPRE 4           // pipeline depth when the activations sit in shared memory
+#endif
+#ifndef SG_ST_STREAM
+#define SG_ST_STREAM 4         // ... when they are streamed beside the weights
+#endif
+#ifndef SG_ST_DEEP
+#define SG_ST_DEEP 8          // ... when there are fewer tiles than SMs (one block per SM)
+#endif
+#ifndef SG_CTAS_PER_SM
+#define SG_CTAS_PER_SM 2
+#endif
 
 enum { SG_STORE = 0, SG_RESIDUAL = 1, SG_SWIGLU = 2, SG_ROPE = 3 };
 
@@ -95,89 +113,22 @@ __device__ __forceinline__ void sg_rows(const SkinnyArgs& p, int tile, int& row_
     }
 }
 
-template <int MT, int EPI>     // MT: tokens padded to 8 * MT
-__global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArgs p) {
-    extern __shared__ __align__(16) unsigned char sg_smem[];
-    constexpr int XR = MT * 8;                       // token rows of a stage
-    constexpr int STAGE_ELEMS = (16 + XR) * SG_LD;
-    bf16* stages = reinterpret_cast<bf16*>(sg_smem);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int row_a, row_b;
-    sg_rows<EPI>(p, blockIdx.x, row_a, row_b);
-    const int nk = (p.K + SG_KB - 1) / SG_KB;
+template <int XR>
+__device__ __forceinline__ float sg_sum(const float* red, int f, int t) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < SG_WARPS; ++w) v += red[(w * 16 + f) * XR + t];
+    return v;
+}
 
-    auto load_stage = [&](int kb, int s) {
-        bf16* ws = stages + s * STAGE_ELEMS;
-        bf16* xs = ws + 16 * SG_LD;
-        const int k0 = kb * SG_KB;
-        // weights: 16 rows x 32 chunks of 16 bytes
-        for (int idx = threadIdx.x; idx < 16 * (SG_KB / 8); idx += SG_THREADS) {
-            const int r = idx / (SG_KB / 8), c = idx - r * (SG_KB / 8);
-            const int k = k0 + c * 8;
-            const int row = (r < 8 ? row_a + r : row_b + r - 8);
-            const bool ok = k < p.K;
-            sg_cp16(sg_smem_u32(ws + r * SG_LD + c * 8), p.w + (size_t)row * p.K + (ok ? k : 0), ok);
-        }
-        for (int idx = threadIdx.x; idx < XR * (SG_KB / 8); idx += SG_THREADS) {
-            const int r = idx / (SG_KB / 8), c = idx - r * (SG_KB / 8);
-            const int k = k0 + c * 8;
-            const bool ok = k < p.K && r < p.M;
-            sg_cp16(sg_smem_u32(xs + r * SG_LD + c * 8), p.x + (size_t)(ok ? r : 0) * p.ldx + (ok ? k : 0), ok);
-        }
-    };
-
-#pragma unroll
-    for (int s = 0; s < SG_STAGES - 1; ++s) {
-        if (s < nk) load_stage(s, s);
-        sg_commit();
-    }
-    float acc[MT][4];
-#pragma unroll
-    for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-
-    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
-    const int b_row = lane & 7, b_col = ((lane >> 3) & 1) * 8;
-    for (int kb = 0; kb < nk; ++kb) {
-        sg_wait<SG_STAGES - 2>();
-        __syncthreads();
-        const int nxt = kb + SG_STAGES - 1;
-        if (nxt < nk) load_stage(nxt, nxt % SG_STAGES);
-        sg_commit();
-        const bf16* ws = stages + (kb % SG_STAGES) * STAGE_ELEMS;
-        const bf16* xs = ws + 16 * SG_LD;
-        const int kw = warp * 64;                    // this warp's slice of the stage
-#pragma unroll
-        for (int ks = 0; ks < 64; ks += 16) {
-            uint32_t a[4];
-            sg_ldmatrix_x4(a, sg_smem_u32(ws + a_row * SG_LD + kw + ks + a_col));
-#pragma unroll
-            for (int nt = 0; nt < MT; ++nt) {
-                uint32_t b[2];
-                sg_ldmatrix_x2(b, sg_smem_u32(xs + (nt * 8 + b_row) * SG_LD + kw + ks + b_col));
-                sg_mma(acc[nt], a, b[0], b[1]);
-            }
-        }
-    }
-    sg_wait<0>();
-    __syncthreads();
-    // add the four warps' sums: red[warp][feature 0..15][token 0..XR-1]
-    float* red = reinterpret_cast<float*>(sg_smem);
-#pragma unroll
-    for (int nt = 0; nt < MT; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int f = (lane >> 2) + (e >> 1) * 8;
-            const int t = nt * 8 + (lane & 3) * 2 + (e & 1);
-            red[(warp * 16 + f) * XR + t] = acc[nt][e];
-        }
-    }
-    __syncthreads();
-
+template <int MT, int EPI>
+__device__ __forceinline__ void sg_epilogue(const SkinnyArgs& p, const float* red, int row_a, int row_b) {
+    constexpr int XR = MT * 8;
     if (EPI == SG_STORE || EPI == SG_RESIDUAL) {
         for (int idx = threadIdx.x; idx < 16 * XR; idx += SG_THREADS) {
             const int t = idx / 16, f = idx - t * 16;          // consecutive threads: consecutive features
             if (t >= p.M) continue;
-            const float v = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+            const float v = sg_sum<XR>(red, f, t);
             const int n = (f < 8 ? row_a + f : row_b + f - 8);
             if (EPI == SG_RESIDUAL) {
                 p.resid[(size_t)t * p.N + n] += v;
@@ -191,9 +142,9 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
         for (int idx = threadIdx.x; idx < 8 * XR; idx += SG_THREADS) {
             const int t = idx / 8, f = idx - t * 8;
             if (t >= p.M) continue;
-            const float gte = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+            const float gte = sg_sum<XR>(red, f, t);
             const int fu = f + 8;
-            const float up = red[fu * XR + t] + red[(16 + fu) * XR + t] + red[(32 + fu) * XR + t] + red[(48 + fu) * XR + t];
+            const float up = sg_sum<XR>(red, fu, t);
             const float sl = gte / (1.0f + expf(-gte));
             reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ld_out + row_a + f] = __float2bfloat16_rn(sl * up);
         }
@@ -205,9 +156,9 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
             for (int idx = threadIdx.x; idx < 8 * XR; idx += SG_THREADS) {
                 const int t = idx / 8, f = idx - t * 8;
                 if (t >= p.M) continue;
-                float x1 = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+                float x1 = sg_sum<XR>(red, f, t);
                 const int fu = f + 8;
-                float x2 = red[fu * XR + t] + red[(16 + fu) * XR + t] + red[(32 + fu) * XR + t] + red[(48 + fu) * XR + t];
+                float x2 = sg_sum<XR>(red, fu, t);
                 if (p.bias) { x1 += p.bias[row_a + f]; x2 += p.bias[row_b + f]; }
                 float y1 = x1, y2 = x2;
                 const int i = d0 + f;                           // pair index
@@ -234,7 +185,7 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
             for (int idx = threadIdx.x; idx < 16 * XR; idx += SG_THREADS) {
                 const int t = idx / 16, f = idx - t * 16;
                 if (t >= p.M || !p.slots || p.slots[t] < 0) continue;
-                float v = red[f * XR + t] + red[(16 + f) * XR + t] + red[(32 + f) * XR + t] + red[(48 + f) * XR + t];
+                float v = sg_sum<XR>(red, f, t);
                 if (p.bias) v += p.bias[row_a + f];
                 const int slot = p.slots[t];
                 p.v_pages[(((size_t)(slot / p.page_size) * p.nkv + kh) * p.page_size + slot % p.page_size) * p.hd + d0 + f] =
@@ -244,18 +195,154 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
     }
 }
 
-static size_t sg_smem_bytes(int mt) { return (size_t)SG_STAGES * (16 + mt * 8) * SG_LD * sizeof(bf16); }
+// XPRE: the activations of all of K are put into shared memory once per block (they are the same
+// for every tile); otherwise each warp streams its slices of them beside the weights.
+template <int MT, int EPI, int STAGES, bool XPRE>     // MT: tokens padded to 8 * MT
+__global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArgs p, int n_tiles, int x_ld) {
+    extern __shared__ __align__(16) unsigned char sg_smem[];
+    constexpr int XR = MT * 8;                               // token rows
+    constexpr int STAGE_ROWS = XPRE ? 16 : 16 + XR;
+    constexpr int STAGE_ELEMS = STAGE_ROWS * SG_LD;          // one warp's stage: rows of 64 + 8 elements
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    bf16* ring = reinterpret_cast<bf16*>(sg_smem) + (size_t)warp * STAGES * STAGE_ELEMS;
+    bf16* x_all = reinterpret_cast<bf16*>(sg_smem) + (size_t)SG_WARPS * STAGES * STAGE_ELEMS;     // XPRE: [XR][x_ld]
+    float* red = reinterpret_cast<float*>(x_all + (XPRE ? (size_t)XR * x_ld : 0));          // [warps][16][XR]
+    const int nk64 = (p.K + SG_KW - 1) / SG_KW;
+    const int nkw = nk64 > warp ? (nk64 - warp + SG_WARPS - 1) / SG_WARPS : 0;     // 64-wide slices of K this warp takes per tile
+    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total = my_tiles * nkw;                            // this warp's pipeline steps
+
+    auto load_step = [&](int it) {
+        const int li = it / nkw, j = it - li * nkw;
+        int ra, rb;
+        sg_rows<EPI>(p, blockIdx.x + li * gridDim.x, ra, rb);
+        bf16* ws = ring + (it % STAGES) * STAGE_ELEMS;
+        const int k0 = (warp + SG_WARPS * j) * SG_KW;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {                            // 16 rows x 8 chunks of 16 bytes
+            const int idx = lane + 32 * q;
+            const int r = idx >> 3, c = idx & 7;
+            const int k = k0 + c * 8;
+            const int row = (r < 8 ? ra + r : rb + r - 8);
+            const bool ok = k < p.K;
+            sg_cp16(sg_smem_u32(ws + r * SG_LD + c * 8), p.w + (size_t)row * p.K + (ok ? k : 0), ok);
+        }
+        if (!XPRE) {
+            bf16* xs = ws + 16 * SG_LD;
+#pragma unroll
+            for (int q = 0; q < MT * 2; ++q) {                   // XR rows x 8 chunks
+                const int idx = lane + 32 * q;
+                const int r = idx >> 3, c = idx & 7;
+                const int k = k0 + c * 8;
+                const bool ok = k < p.K && r < p.M;
+                sg_cp16(sg_smem_u32(xs + r * SG_LD + c * 8), p.x + (size_t)(ok ? r : 0) * p.ldx + (ok ? k : 0), ok);
+            }
+        }
+    };
+
+    if (XPRE) {
+        const int chunks = (nk64 * SG_KW) >> 3;                  // per row, K rounded up to 64
+        for (int idx = threadIdx.x; idx < XR * chunks; idx += SG_THREADS) {
+            const int r = idx / chunks, c = idx - r * chunks;
+            const int k = c * 8;
+            const bool ok = k < p.K && r < p.M;
+            sg_cp16(sg_smem_u32(x_all + r * x_ld + k), p.x + (size_t)(ok ? r : 0) * p.ldx + (ok ? k : 0), ok);
+        }
+    }
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < total) load_step(s);
+        sg_commit();
+    }
+    if (XPRE) {
+        sg_wait<0>();            // once per block: the activations (and the first weight stages) have landed
+        __syncthreads();
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_row = lane & 7, b_col = ((lane >> 3) & 1) * 8;
+    int it = 0;
+    for (int li = 0; li < my_tiles; ++li) {
+        for (int j = 0; j < nkw; ++j, ++it) {
+            sg_wait<STAGES - 2>();
+            __syncwarp();
+            if (it + STAGES - 1 < total) load_step(it + STAGES - 1);
+            sg_commit();
+            const bf16* ws = ring + (it % STAGES) * STAGE_ELEMS;
+            const bf16* xs = XPRE ? x_all + (warp + SG_WARPS * j) * SG_KW : ws + 16 * SG_LD;
+            const int xld = XPRE ? x_ld : SG_LD;
+#pragma unroll
+            for (int ks = 0; ks < SG_KW; ks += 16) {
+                uint32_t a[4];
+                sg_ldmatrix_x4(a, sg_smem_u32(ws + a_row * SG_LD + ks + a_col));
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) {
+                    uint32_t b[2];
+                    sg_ldmatrix_x2(b, sg_smem_u32(xs + (nt * 8 + b_row) * xld + ks + b_col));
+                    sg_mma(acc[nt], a, b[0], b[1]);
+                }
+            }
+        }
+        // the tile is complete: add the four warps' sums (red[warp][feature 0..15][token 0..XR-1])
+        int row_a, row_b;
+        sg_rows<EPI>(p, blockIdx.x + li * gridDim.x, row_a, row_b);
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int f = (lane >> 2) + (e >> 1) * 8;
+                const int t = nt * 8 + (lane & 3) * 2 + (e & 1);
+                red[(warp * 16 + f) * XR + t] = acc[nt][e];
+                acc[nt][e] = 0.f;
+            }
+        }
+        __syncthreads();
+        sg_epilogue<MT, EPI>(p, red, row_a, row_b);
+        __syncthreads();         // red is written again at the end of the next tile
+    }
+    sg_wait<0>();
+}
+
+static int sg_num_sms() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+template <int MT, int EPI, int STAGES, bool XPRE>
+static void sg_launch_one(const SkinnyArgs& a, int tiles, int grid, cudaStream_t stream) {
+    const int x_ld = ((a.K + SG_KW - 1) / SG_KW) * SG_KW + 8;
+    const size_t smem = (size_t)SG_WARPS * STAGES * (XPRE ? 16 : 16 + MT * 8) * SG_LD * sizeof(bf16) +
+                        (XPRE ? (size_t)MT * 8 * x_ld * sizeof(bf16) : 0) + (size_t)SG_WARPS * 16 * MT * 8 * sizeof(float);
+    cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI, STAGES, XPRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    skinny_gemm_kernel<MT, EPI, STAGES, XPRE><<<grid, SG_THREADS, smem, stream>>>(a, tiles, x_ld);
+}
 
 template <int EPI>
 static int sg_launch(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
     const int mt = (a.M + 7) / 8;
-    const size_t smem = sg_smem_bytes(mt);
+    const int sms = sg_num_sms();
+    // persistent blocks, SG_CTAS_PER_SM per SM
+    const int grid = tiles < SG_CTAS_PER_SM * sms ? tiles : SG_CTAS_PER_SM * sms;
+    // the activations of all of K stay in shared memory when they fit beside the weight rings
+    const bool xpre = (size_t)mt * 8 * (a.K + 72) * sizeof(bf16) <= 34 * 1024;
+    // fewer tiles than SMs and a long K: one block per SM has to keep enough bytes in flight alone
+    const bool deep = !xpre && tiles <= sms;
     if (mt == 1) {
-        cudaFuncSetAttribute(skinny_gemm_kernel<1, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        skinny_gemm_kernel<1, EPI><<<tiles, SG_THREADS, smem, stream>>>(a);
+        if (xpre) sg_launch_one<1, EPI, SG_ST_XPRE, true>(a, tiles, grid, stream);
+        else if (deep) sg_launch_one<1, EPI, SG_ST_DEEP, false>(a, tiles, grid, stream);
+        else sg_launch_one<1, EPI, SG_ST_STREAM, false>(a, tiles, grid, stream);
     } else if (mt == 2) {
-        cudaFuncSetAttribute(skinny_gemm_kernel<2, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        skinny_gemm_kernel<2, EPI><<<tiles, SG_THREADS, smem, stream>>>(a);
+        if (xpre) sg_launch_one<2, EPI, SG_ST_XPRE, true>(a, tiles, grid, stream);
+        else if (deep) sg_launch_one<2, EPI, SG_ST_DEEP * 3 / 4, false>(a, tiles, grid, stream);
+        else sg_launch_one<2, EPI, SG_ST_STREAM * 3 / 4, false>(a, tiles, grid, stream);
     } else
         return PICO_ERR_SIZE;
     return pico_launch_status();
