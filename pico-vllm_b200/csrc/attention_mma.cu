@@ -20,6 +20,7 @@
 
 #define MMA_BN 64          // cache positions per shared-memory tile
 #define MMA_THREADS 128    // 4 warps
+#define DEC_STAGES 3       // tiles in flight in the decode kernel
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -48,25 +49,53 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// How a block's threads share the 16-byte pieces of a tile: a power-of-two number of threads per
+// row (at least hd/8 pieces), so that no division is needed per piece.  page_shift >= 0 when the
+// page size is a power of two.
+struct TileMap {
+    int chunks;        // 16-byte pieces per row (hd / 8)
+    int c;             // this thread's piece of a row (may be >= chunks: the thread then idles)
+    int row0, rstep;   // first row and row step of this thread
+    int page_shift, page_size;
+};
+__device__ __forceinline__ TileMap make_tile_map(int hd, int page_size) {
+    TileMap tm;
+    tm.chunks = hd >> 3;
+    int sh = 1;
+    while ((1 << sh) < tm.chunks) ++sh;             // threads per row = 2^sh (2 .. 32)
+    tm.c = threadIdx.x & ((1 << sh) - 1);
+    tm.row0 = threadIdx.x >> sh;
+    tm.rstep = MMA_THREADS >> sh;
+    tm.page_size = page_size;
+    tm.page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+    return tm;
+}
+
 // Loads keys (or values) of cache positions n0 .. n0+MMA_BN-1 of one key/value head into a
 // shared tile [MMA_BN][ld] (ld = hd + 8 elements: the 16 bytes of padding make ldmatrix free of
 // bank conflicts for every hd that is a multiple of 16).  Positions outside [n_lo, n_hi) are
 // filled with zeros and their pages are not touched.
 __device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ pages, const int* __restrict__ table,
                                              int n0, int n_lo, int n_hi, int kh, int nkv, int hd, int ld,
-                                             int page_size) {
-    const int chunks = hd >> 3;                 // 16-byte pieces per row
-    const int total = MMA_BN * chunks;
-    for (int idx = threadIdx.x; idx < total; idx += MMA_THREADS) {
-        const int key = idx / chunks, c = idx - key * chunks;
+                                             const TileMap& tm) {
+    if (tm.c >= tm.chunks) return;
+    for (int key = tm.row0; key < MMA_BN; key += tm.rstep) {
         const int n = n0 + key;
         const bool ok = n >= n_lo && n < n_hi;
         const bf16* src = pages;
         if (ok) {
-            const int page = table[n / page_size];
-            src = pages + (((size_t)page * nkv + kh) * page_size + (n % page_size)) * hd + c * 8;
+            int page, off;
+            if (tm.page_shift >= 0) {
+                page = table[n >> tm.page_shift];
+                off = n & (tm.page_size - 1);
+            } else {
+                const int blk = n / tm.page_size;
+                page = table[blk];
+                off = n - blk * tm.page_size;
+            }
+            src = pages + (((size_t)page * nkv + kh) * tm.page_size + off) * hd + tm.c * 8;
         }
-        cp_async_16(smem_u32(tile + key * ld + c * 8), src, ok);
+        cp_async_16(smem_u32(tile + key * ld + tm.c * 8), src, ok);
     }
 }
 
@@ -174,6 +203,7 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
     const int hi = pos0 + ntok;                     // one past the last visible key of the tile
     const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
     const int ld = hd + 8;
+    const TileMap tm = make_tile_map(hd, page_size);
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);              // [64][ld]
     bf16* k_s = q_s + 64 * ld;                                  // [2][MMA_BN][ld]
     bf16* v_s = k_s + 2 * MMA_BN * ld;                          // [2][MMA_BN][ld]
@@ -190,8 +220,8 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
         cp_async_16(smem_u32(q_s + r * ld + c * 8), src, ok);
     }
     const int ntiles = (hi - lo + MMA_BN - 1) / MMA_BN;
-    load_kv_tile(k_s, k_pages, table, lo, lo, hi, kh, nkv, hd, ld, page_size);
-    load_kv_tile(v_s, v_pages, table, lo, lo, hi, kh, nkv, hd, ld, page_size);
+    load_kv_tile(k_s, k_pages, table, lo, lo, hi, kh, nkv, hd, ld, tm);
+    load_kv_tile(v_s, v_pages, table, lo, lo, hi, kh, nkv, hd, ld, tm);
     cp_async_commit();
 
     float o[HD_MAX / 8][4];
@@ -215,8 +245,8 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
         const int n0 = lo + t * MMA_BN;
         const int buf = t & 1;
         if (t + 1 < ntiles) {
-            load_kv_tile(k_s + (buf ^ 1) * MMA_BN * ld, k_pages, table, n0 + MMA_BN, lo, hi, kh, nkv, hd, ld, page_size);
-            load_kv_tile(v_s + (buf ^ 1) * MMA_BN * ld, v_pages, table, n0 + MMA_BN, lo, hi, kh, nkv, hd, ld, page_size);
+            load_kv_tile(k_s + (buf ^ 1) * MMA_BN * ld, k_pages, table, n0 + MMA_BN, lo, hi, kh, nkv, hd, ld, tm);
+            load_kv_tile(v_s + (buf ^ 1) * MMA_BN * ld, v_pages, table, n0 + MMA_BN, lo, hi, kh, nkv, hd, ld, tm);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -282,9 +312,10 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
     const int end = min(hi, begin + per * MMA_BN);
     const int ntiles = end > begin ? (end - begin + MMA_BN - 1) / MMA_BN : 0;
     const int ld = hd + 8;
+    const TileMap tm = make_tile_map(hd, page_size);
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);              // [16][ld]
-    bf16* k_s = q_s + 16 * ld;                                  // [2][MMA_BN][ld]
-    bf16* v_s = k_s + 2 * MMA_BN * ld;
+    bf16* k_s = q_s + 16 * ld;                                  // [DEC_STAGES][MMA_BN][ld]
+    bf16* v_s = k_s + DEC_STAGES * MMA_BN * ld;
     const int* table = block_table + (size_t)tok_seg[t] * table_stride;
 
     const int chunks = hd >> 3;
@@ -294,11 +325,15 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
         const bf16* src = q + (size_t)t * q_row_stride + (size_t)(kh * g + (ok ? r : 0)) * hd + c * 8;
         cp_async_16(smem_u32(q_s + r * ld + c * 8), src, ok);
     }
-    if (ntiles > 0) {
-        load_kv_tile(k_s, k_pages, table, begin, begin, end, kh, nkv, hd, ld, page_size);
-        load_kv_tile(v_s, v_pages, table, begin, begin, end, kh, nkv, hd, ld, page_size);
+    // the first DEC_STAGES-1 tiles are requested at once; queries ride with the first group
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+        if (st < ntiles) {
+            load_kv_tile(k_s + st * MMA_BN * ld, k_pages, table, begin + st * MMA_BN, begin, end, kh, nkv, hd, ld, tm);
+            load_kv_tile(v_s + st * MMA_BN * ld, v_pages, table, begin + st * MMA_BN, begin, end, kh, nkv, hd, ld, tm);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
 
     float o[HD_MAX / 8][4];
 #pragma unroll
@@ -307,16 +342,18 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
 
     for (int it = 0; it < ntiles; ++it) {
         const int n0 = begin + it * MMA_BN;
-        const int buf = it & 1;
-        if (it + 1 < ntiles) {
-            load_kv_tile(k_s + (buf ^ 1) * MMA_BN * ld, k_pages, table, n0 + MMA_BN, begin, end, kh, nkv, hd, ld, page_size);
-            load_kv_tile(v_s + (buf ^ 1) * MMA_BN * ld, v_pages, table, n0 + MMA_BN, begin, end, kh, nkv, hd, ld, page_size);
+        const int buf = it % DEC_STAGES;
+        cp_async_wait<DEC_STAGES - 2>();
+        __syncthreads();                                // tile `it` has landed; everyone is done with tile it-1
+        {
+            const int nx = it + DEC_STAGES - 1;         // goes into the buffer tile it-1 used
+            if (nx < ntiles) {
+                const int nb = nx % DEC_STAGES;
+                load_kv_tile(k_s + nb * MMA_BN * ld, k_pages, table, begin + nx * MMA_BN, begin, end, kh, nkv, hd, ld, tm);
+                load_kv_tile(v_s + nb * MMA_BN * ld, v_pages, table, begin + nx * MMA_BN, begin, end, kh, nkv, hd, ld, tm);
+            }
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
-        __syncthreads();
         const int w0 = n0 + warp * 16;              // this warp's 16 positions of the tile
         if (w0 < end) {
             float s[2][4];
@@ -333,7 +370,6 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
             online_softmax<HD_MAX, 2>(s, m, l, o);
             pv_tile<HD_MAX, 2>(o, s, v_s + (buf * MMA_BN + warp * 16) * ld, hd, ld, lane);
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -387,33 +423,42 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
 }
 
 // out[t, h, :] = sum_i o_i e^(m_i - M) / sum_i l_i e^(m_i - M) over the splits i of a listed token.
+// One block per (token, head): the first warp turns the splits' (m, l) into weights e^(m_i - M) / L,
+// then every thread sums its head dimensions over the splits (independent, coalesced loads).
+#define COMBINE_MAX_SPLITS 64
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       bf16* __restrict__ out, const int* __restrict__ tok_list, int nh, int hd,
                                       int n_splits) {
+    __shared__ float wgt[COMBINE_MAX_SPLITS];
     const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x;
     const size_t th = (size_t)t * nh + blockIdx.y;
     const float* ml = part_ml + th * n_splits * 2;
-    float M = -INFINITY;
-    for (int i = 0; i < n_splits; ++i) M = fmaxf(M, ml[2 * i]);
-    float L = 0.f;
-    for (int i = 0; i < n_splits; ++i) {
-        const float mi = ml[2 * i];
-        if (mi != -INFINITY) L += ml[2 * i + 1] * expf(mi - M);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float m0 = lane < n_splits ? ml[2 * lane] : -INFINITY;
+        const float m1 = lane + 32 < n_splits ? ml[2 * (lane + 32)] : -INFINITY;
+        const float l0 = lane < n_splits ? ml[2 * lane + 1] : 0.f;
+        const float l1 = lane + 32 < n_splits ? ml[2 * (lane + 32) + 1] : 0.f;
+        const float M = warp_max(fmaxf(m0, m1));
+        const float e0 = m0 == -INFINITY ? 0.f : expf(m0 - M), e1 = m1 == -INFINITY ? 0.f : expf(m1 - M);
+        const float L = warp_sum(l0 * e0 + l1 * e1);
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        wgt[lane] = e0 * inv;
+        wgt[lane + 32] = e1 * inv;
     }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    __syncthreads();
+    const float* po = part_o + th * n_splits * hd;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc = 0.f;
-        for (int i = 0; i < n_splits; ++i) {
-            const float mi = ml[2 * i];
-            if (mi != -INFINITY) acc += part_o[(th * n_splits + i) * hd + d] * expf(mi - M);
-        }
-        out[th * hd + d] = __float2bfloat16_rn(acc * inv);
+#pragma unroll 8
+        for (int i = 0; i < n_splits; ++i) acc += po[(size_t)i * hd + d] * wgt[i];
+        out[th * hd + d] = __float2bfloat16_rn(acc);
     }
 }
 
 static size_t prefill_smem(int hd) { return (size_t)(64 + 4 * MMA_BN) * (hd + 8) * sizeof(bf16); }
 static size_t decode_smem(int hd) {
-    const size_t tiles = (size_t)(16 + 4 * MMA_BN) * (hd + 8) * sizeof(bf16);
+    const size_t tiles = (size_t)(16 + 2 * DEC_STAGES * MMA_BN) * (hd + 8) * sizeof(bf16);
     const size_t merge = (size_t)16 * (hd + 8) * sizeof(bf16) + (size_t)4 * 16 * (hd + 2) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
@@ -459,7 +504,7 @@ PICO_API int pico_paged_decode_mma(const void* q, int q_row_stride, const void* 
     if (n_tok <= 0) return 0;
     if (hd % 16 != 0 || hd < 16 || hd > 256 || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
-    if (g > 16 || nkv > 65535 || n_tok > 65535 || n_splits < 1) return PICO_ERR_SIZE;
+    if (g > 16 || nkv > 65535 || n_tok > 65535 || n_splits < 1 || n_splits > COMBINE_MAX_SPLITS) return PICO_ERR_SIZE;
     if (n_splits > 1 && (!part_o || !part_ml)) return PICO_ERR_SIZE;
     if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
     const dim3 grid(n_splits, nkv, n_tok);

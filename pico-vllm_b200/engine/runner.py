@@ -105,11 +105,12 @@ class ModelRunner:
         return self._stage
 
     def _splits(self, T: int, max_kv: int) -> int:
-        """How many parts to cut each token's key range into: enough blocks to fill the GPU
-        when the batch is small and the context long."""
+        """How many parts to cut each token's key range into: as many as make one wave of blocks
+        (two per SM on 148 SMs) when the batch is small and the context long, each part at least
+        two tiles of 64 keys."""
         blocks = max(1, T * self._min_kv_heads)
-        want = -(-592 // blocks)                      # ~4 blocks per SM on 148 SMs
-        most = max(1, max_kv // 128)
+        want = 296 // blocks
+        most = max_kv // 128
         return int(max(1, min(want, most, 64)))
 
     def _scratch_for(self, T: int, splits: int) -> Optional[torch.Tensor]:
