@@ -216,8 +216,12 @@ class CacheManager:
             if eid in self.entry_group:
                 gi, idx = self.entry_group[eid]
                 g = self.groups[gi]
-                out.append(CacheView(group=gi, k=None if g.k is None else g.k[idx],
-                                     v=None if g.v is None else g.v[idx], page_size=self.page_size))
+                view = CacheView(group=gi, k=None if g.k is None else g.k[idx],
+                                 v=None if g.v is None else g.v[idx], page_size=self.page_size)
+                if g.k is not None and g.k.is_cuda and g.k.dtype == torch.bfloat16:
+                    from .. import ops
+                    view.k_map, view.v_map = ops.make_kv_tensor_map(view.k), ops.make_kv_tensor_map(view.v)
+                out.append(view)
             else:
                 out.append(CacheView(state=self.states.get(eid)))
         return out

@@ -58,6 +58,8 @@ __global__ void paged_attention_generic_kernel(
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ tok_seg, const int* __restrict__ positions, const int* __restrict__ block_table,
     int table_stride, int nh, int nkv, int hd, int page_size, int window, float scale, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float q_s[];  // [warps][hd]
     const int t = blockIdx.x, kh = blockIdx.y, sp = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -143,6 +145,8 @@ __global__ void paged_attention_generic_kernel(
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          T* __restrict__ out, int hd, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t th = blockIdx.x;  // t * nh + h
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
@@ -182,17 +186,17 @@ PICO_API int pico_paged_attention_generic(const void* q, int q_row_stride, const
     const size_t smem = (size_t)warps * hd * sizeof(float);
     if (act_dtype == PICO_F32) {
         if ((q_row_stride % 4) != 0) return PICO_ERR_ALIGN;
-        paged_attention_generic_kernel<float><<<grid, warps * 32, smem, stream>>>(
+        pico_launch((paged_attention_generic_kernel<float>), dim3(grid), dim3(warps * 32), smem, stream, 
             (const float*)q, q_row_stride, (const float*)k_pages, (const float*)v_pages, (float*)out, part_o,
             part_ml, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits);
         if (n_splits > 1)
-            attention_combine_kernel<float><<<T * nh, 64, 0, stream>>>(part_o, part_ml, (float*)out, hd, n_splits);
+            pico_launch((attention_combine_kernel<float>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (float*)out, hd, n_splits);
     } else if (act_dtype == PICO_BF16) {
-        paged_attention_generic_kernel<bf16><<<grid, warps * 32, smem, stream>>>(
+        pico_launch((paged_attention_generic_kernel<bf16>), dim3(grid), dim3(warps * 32), smem, stream, 
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, part_o, part_ml,
             tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale, n_splits);
         if (n_splits > 1)
-            attention_combine_kernel<bf16><<<T * nh, 64, 0, stream>>>(part_o, part_ml, (bf16*)out, hd, n_splits);
+            pico_launch((attention_combine_kernel<bf16>), dim3(T * nh), dim3(64), 0, stream, part_o, part_ml, (bf16*)out, hd, n_splits);
     } else
         return PICO_ERR_DTYPE;
     return pico_launch_status();

@@ -18,36 +18,7 @@
 // (attention.py:167-169); here tiles beyond the last visible key are never loaded.
 #include "common.cuh"
 
-#define MMA_BN 64          // cache positions per shared-memory tile
-#define MMA_THREADS 128    // 4 warps
-#define DEC_STAGES 3       // tiles in flight in the decode kernel
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool pred) {
-    const int n = pred ? 16 : 0;   // src-size 0: the 16 bytes are filled with zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
+#include "mma_helpers.cuh"
 
 // How a block's threads share the 16-byte pieces of a tile: a power-of-two number of threads per
 // row (at least hd/8 pieces), so that no division is needed per piece.  page_shift >= 0 when the
@@ -145,41 +116,6 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD_MAX / 8][4], const float (
     }
 }
 
-// Running softmax over one tile of scores for the two rows a thread holds (lane/4 and lane/4+8).
-// s: scores already scaled to log2 units and masked with -inf.  On return s holds p = 2^(s - m).
-template <int HD_MAX, int NT>
-__device__ __forceinline__ void online_softmax(float (&s)[NT][4], float (&m)[2], float (&l)[2],
-                                               float (&o)[HD_MAX / 8][4]) {
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        float mx = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < NT; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * r], s[j][2 * r + 1]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m[r], mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
-        const float corr = exp2f(m[r] - m_use);                      // m = -inf gives 0
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const float p0 = exp2f(s[j][2 * r] - m_use), p1 = exp2f(s[j][2 * r + 1] - m_use);
-            s[j][2 * r] = p0;
-            s[j][2 * r + 1] = p1;
-            sum += p0 + p1;
-        }
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        l[r] = l[r] * corr + sum;
-        m[r] = m_new;
-#pragma unroll
-        for (int i = 0; i < HD_MAX / 8; ++i) {
-            o[i][2 * r] *= corr;
-            o[i][2 * r + 1] *= corr;
-        }
-    }
-}
-
 // ------------------------------------------------------------------------------------------ prefill
 // grid: (tiles of tokens, kv heads, listed segments).  A block takes `tpt` = 64 / g tokens of one
 // segment and the g query heads of one kv head: 64 rows, 16 per warp.
@@ -190,6 +126,8 @@ paged_prefill_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf1
                          const int* __restrict__ cu_q, const int* __restrict__ positions,
                          const int* __restrict__ block_table, int table_stride, int nh, int nkv, int hd,
                          int page_size, int window, float scale_log2) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int g = nh / nkv;
     const int tpt = 64 / g;                         // tokens per tile (g <= 64)
@@ -298,6 +236,8 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                         const int* __restrict__ tok_seg, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_stride, int nh, int nkv, int hd,
                         int page_size, int window, float scale_log2, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int g = nh / nkv;
     const int t = tok_list ? tok_list[blockIdx.z] : blockIdx.z;
@@ -429,6 +369,8 @@ paged_decode_mma_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       bf16* __restrict__ out, const int* __restrict__ tok_list, int nh, int hd,
                                       int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float wgt[COMBINE_MAX_SPLITS];
     const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x;
     const size_t th = (size_t)t * nh + blockIdx.y;
@@ -454,6 +396,13 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
         for (int i = 0; i < n_splits; ++i) acc += po[(size_t)i * hd + d] * wgt[i];
         out[th * hd + d] = __float2bfloat16_rn(acc);
     }
+}
+
+int pico_launch_decode_combine(const float* part_o, const float* part_ml, void* out, const int* tok_list, int n_tok,
+                               int nh, int hd, int n_splits, cudaStream_t stream) {
+    pico_launch(decode_combine_kernel, dim3(dim3(n_tok, nh)), dim3(hd >= 128 ? 128 : 64), 0, stream, part_o, part_ml, (bf16*)out, tok_list,
+                                                                           nh, hd, n_splits);
+    return pico_launch_status();
 }
 
 static size_t prefill_smem(int hd) { return (size_t)(64 + 4 * MMA_BN) * (hd + 8) * sizeof(bf16); }
@@ -482,7 +431,7 @@ PICO_API int pico_paged_prefill_mma(const void* q, int q_row_stride, const void*
 #define LAUNCH_PREFILL(HD)                                                                                          \
     do {                                                                                                            \
         cudaFuncSetAttribute(paged_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        paged_prefill_mma_kernel<HD><<<grid, MMA_THREADS, smem, stream>>>(                                          \
+        pico_launch((paged_prefill_mma_kernel<HD>), dim3(grid), dim3(MMA_THREADS), smem, stream,                                           \
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seg_list, cu_q,   \
             positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2);                      \
     } while (0)
@@ -513,7 +462,7 @@ PICO_API int pico_paged_decode_mma(const void* q, int q_row_stride, const void* 
 #define LAUNCH_DECODE(HD)                                                                                          \
     do {                                                                                                           \
         cudaFuncSetAttribute(paged_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        paged_decode_mma_kernel<HD><<<grid, MMA_THREADS, smem, stream>>>(                                          \
+        pico_launch((paged_decode_mma_kernel<HD>), dim3(grid), dim3(MMA_THREADS), smem, stream,                                           \
             (const bf16*)q, q_row_stride, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, part_o, part_ml, \
             tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, hd, page_size, window, scale_log2,   \
             n_splits);                                                                                             \
@@ -522,8 +471,6 @@ PICO_API int pico_paged_decode_mma(const void* q, int q_row_stride, const void* 
     else if (hd <= 128) LAUNCH_DECODE(128);
     else LAUNCH_DECODE(256);
 #undef LAUNCH_DECODE
-    if (n_splits > 1)
-        decode_combine_kernel<<<dim3(n_tok, nh), hd >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, tok_list,
-                                                                               nh, hd, n_splits);
+    if (n_splits > 1) return pico_launch_decode_combine(part_o, part_ml, out, tok_list, n_tok, nh, hd, n_splits, stream);
     return pico_launch_status();
 }

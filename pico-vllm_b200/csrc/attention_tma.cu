@@ -1,0 +1,384 @@
+// Single-token ("decode") paged attention for bfloat16 with the cache pages brought in by TMA.
+//
+// A cache page of one key/value head is a contiguous [page_size, head_dim] block, so a tile of 64
+// cache positions is 64 / page_size boxes of a 2-D tensor map over the layer's pages
+// ([pages * kv_heads * page_size rows, head_dim]); one box is a whole page of one head and lands in
+// shared memory in the 128-byte swizzle, which ldmatrix then reads with few bank conflicts.  A
+// producer warp issues the copies (cp.async.bulk.tensor.3d, completion on an mbarrier) while four
+// consumer warps multiply, so neither the per-16-byte address arithmetic of a cp.async pipeline -
+// which made the earlier kernel instruction-bound - nor the issue of the copies sits in the
+// consumers' way; full/empty mbarriers per stage replace block-wide barriers.  Everything else is
+// as in attention_mma.cu: the g <= 16 query heads of a key/value head form one 16-row tile,
+// mma.sync m16n8k16 with float32 accumulation, running max/sum softmax in float32, the key range
+// of a token cut into n_splits parts whose partial results a second kernel combines.
+//
+// Formulas restated from the reference as cited in attention_mma.cu
+// (pico_vllm/kernels/attention.py:31, 67-82, 92).  Every wait on an mbarrier is bounded: after
+// TMA_WAIT_LIMIT polls the block records an error in a status word, stops issuing copies and
+// leaves (its results are then invalid; the host reads the word with pico_tma_status).
+#include <cuda.h>
+#include "mma_helpers.cuh"
+
+#ifndef TMA_STAGES
+#define TMA_STAGES 3
+#endif
+#define TMA_WAIT_LIMIT (1 << 22)
+#ifndef TMA_L2_PROMO
+#define TMA_L2_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
+#define TMA_TABLE_CACHE 1024       // block-table entries of a block's key range kept in shared memory
+
+__device__ int g_tma_status = 0;     // 0 = fine; 1 = a wait on a TMA copy ran out
+
+PICO_API int pico_tma_status(int* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_tma_status, sizeof(int), 0, cudaMemcpyDeviceToHost);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (int i = 0; i < TMA_WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+// A tile is [64 cache positions][HD] bfloat16, rows of HD*2 bytes, made of 128-byte segments that
+// TMA stores in its 128-byte swizzle: the 16-byte piece c of segment number s (counted from the
+// tile's 1024-byte aligned start) sits at piece position c ^ (s & 7).
+template <int HD>
+__device__ __forceinline__ uint32_t swz_addr(uint32_t tile, int key, int dim) {
+    const int seg = key * (HD / 64) + (dim >> 6), chunk = (dim & 63) >> 3;
+    return tile + seg * 128 + ((chunk ^ (seg & 7)) << 4);
+}
+
+// 4 consumer warps (multiply) + 1 producer warp (one lane issues the TMA copies).  full[s]: the
+// copies of stage s have landed (transaction count); empty[s]: the four consumer warps are done
+// with stage s.
+#define TMA_THREADS 160
+template <int HD>     // head size: 64 or 128 (a multiple of 64)
+__global__ void __launch_bounds__(TMA_THREADS)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                        const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_list,
+                        const int* __restrict__ tok_seg, const int* __restrict__ positions,
+                        const int* __restrict__ block_table, int table_stride, int nh, int nkv, int page_size,
+                        int window, float scale_log2, int n_splits) {
+    pdl_launch_dependents();
+    extern __shared__ unsigned char smem_dyn[];
+    constexpr int TILE_BYTES = MMA_BN * HD * 2;                  // one K or V tile
+    constexpr int QLD = HD + 8;
+    // the swizzle pattern follows shared-memory address bits 7..9: tiles start on 1024 bytes
+    unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    // [stages][K tile | V tile], then the queries, the barriers, the block-table entries
+    unsigned char* tiles = smem_raw;
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw + TMA_STAGES * 2 * TILE_BYTES);     // [16][QLD]
+    uint64_t* full = reinterpret_cast<uint64_t*>(q_s + 16 * QLD);                    // [stages]
+    uint64_t* empty = full + TMA_STAGES;                                             // [stages]
+    volatile int* abort_s = reinterpret_cast<volatile int*>(empty + TMA_STAGES);
+    int* tbl_s = const_cast<int*>(abort_s) + 2;                                      // [TMA_TABLE_CACHE]
+    const int g = nh / nkv;
+    const int kh = blockIdx.y, sp = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < TMA_STAGES; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 4);
+        }
+        *abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    pdl_wait();             // everything below reads what earlier kernels and copies wrote
+    const int t = tok_list ? tok_list[blockIdx.z] : blockIdx.z;
+    const int pos = positions[t];
+    const int hi = pos + 1;                                      // pos = -1 (padding): no keys at all
+    const int lo = (window > 0 && hi > window) ? hi - window : 0;
+    // tiles are aligned to multiples of 64 cache positions, so that a tile is whole pages
+    const int tile_lo = lo / MMA_BN, tile_hi = (hi + MMA_BN - 1) / MMA_BN;
+    const int per = (tile_hi - tile_lo + n_splits - 1) / n_splits;
+    const int t_begin = tile_lo + sp * per;
+    const int t_end = min(tile_hi, t_begin + per);
+    const int ntiles = t_end > t_begin ? t_end - t_begin : 0;
+    const int* table = block_table + (size_t)tok_seg[t] * table_stride;
+    const int ppt = MMA_BN / page_size;                          // pages per tile
+    {   // the block-table entries of this block's range, read once and together
+        const int first_entry = t_begin * ppt;
+        const int n_entries = min(ntiles * ppt, TMA_TABLE_CACHE);
+        for (int i = threadIdx.x; i < n_entries; i += TMA_THREADS)
+            tbl_s[i] = first_entry + i < table_stride ? table[first_entry + i] : 0;
+    }
+    __syncthreads();                                             // barriers are initialised, the table is there
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            for (int it = 0; it < ntiles; ++it) {
+                const int s = it % TMA_STAGES;
+                if (it >= TMA_STAGES && !mbar_wait(empty + s, ((it / TMA_STAGES) - 1) & 1)) {
+                    g_tma_status = 1;
+                    *abort_s = 1;
+                }
+                if (*abort_s) break;
+                const int n0 = (t_begin + it) * MMA_BN;
+                unsigned char* kt = tiles + (size_t)s * 2 * TILE_BYTES;
+                unsigned char* vt = kt + TILE_BYTES;
+                // pages wholly outside [lo, hi) are skipped: they may have been given back (a window) or
+                // not exist yet
+                int first = 0, last = ppt;
+                while (first < last && n0 + (first + 1) * page_size <= lo) ++first;
+                while (last > first && n0 + (last - 1) * page_size >= hi) --last;
+                mbar_expect_tx(full + s, (uint32_t)((last - first) * page_size * HD * 2 * 2));
+                for (int pg = first; pg < last; ++pg) {
+                    const int e = it * ppt + pg;
+                    const int page = e < TMA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
+                    const int row = (page * nkv + kh) * page_size;
+                    tma_load_3d(kt + pg * page_size * HD * 2, &k_map, 0, 0, row, full + s);
+                    tma_load_3d(vt + pg * page_size * HD * 2, &v_map, 0, 0, row, full + s);
+                }
+            }
+        }
+        return;
+    }
+    // -------------------------------------------------------------------- consumers (warps 0..3)
+    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
+        const int r = idx / (HD / 8), c = idx - r * (HD / 8);
+        const bool ok = r < g;
+        const bf16* src = q + (size_t)t * q_row_stride + (size_t)(kh * g + (ok ? r : 0)) * HD + c * 8;
+        cp_async_16(smem_u32(q_s + r * QLD + c * 8), src, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    consumer_sync();                                             // the queries are in shared memory
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+    const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
+
+    for (int it = 0; it < ntiles; ++it) {
+        const int s = it % TMA_STAGES;
+        const int n0 = (t_begin + it) * MMA_BN;
+        if (!mbar_wait(full + s, (it / TMA_STAGES) & 1)) {
+            g_tma_status = 1;
+            *abort_s = 1;
+        }
+        if (*abort_s) break;
+        const uint32_t kt = smem_u32(tiles + (size_t)s * 2 * TILE_BYTES);
+        const uint32_t vt = kt + TILE_BYTES;
+        const int kw = warp * 16;                                // this warp's 16 positions of the tile
+        const int w0 = n0 + kw;
+        if (w0 < hi && w0 + 16 > lo) {
+            float sc[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+            for (int k0 = 0; k0 < HD; k0 += 16) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4(a, smem_u32(q_s + a_row * QLD + k0 + a_col));
+                ldmatrix_x4(b, swz_addr<HD>(kt, kw + b_row, k0 + b_col));
+                mma_bf16(sc[0], a, b[0], b[1]);
+                mma_bf16(sc[1], a, b[2], b[3]);
+            }
+            bool edge = false;                                   // some of the 16 positions are not visible
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int n = w0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const bool vis = n >= lo && n < hi;
+                    edge |= !vis;
+                    sc[j][e] = vis ? sc[j][e] * scale_log2 : -INFINITY;
+                }
+            online_softmax<HD, 2>(sc, m, l, o);
+            // p.v: invisible positions have p = 0 exactly, but their value rows may hold anything
+            // (another request's data, or not-a-number): they are read as zero
+            const bool warp_edge = __any_sync(0xffffffffu, edge);
+            uint32_t a[4];
+            a[0] = pack_bf16(sc[0][0], sc[0][1]);
+            a[1] = pack_bf16(sc[0][2], sc[0][3]);
+            a[2] = pack_bf16(sc[1][0], sc[1][1]);
+            a[3] = pack_bf16(sc[1][2], sc[1][3]);
+            const int vkey = kw + v_row;
+#pragma unroll
+            for (int d0 = 0; d0 < HD; d0 += 16) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, swz_addr<HD>(vt, vkey, d0 + v_col));
+                if (warp_edge) {
+                    // after the transposing load, register j of lane L holds the values of cache
+                    // positions w0 + (j&1)*8 + (L%4)*2 + {0, 1} (low and high half): clear by position
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int key0 = n0 + kw + (j & 1) * 8 + (lane & 3) * 2;
+                        const bool ok0 = key0 >= lo && key0 < hi, ok1 = key0 + 1 >= lo && key0 + 1 < hi;
+                        b[j] &= (ok0 ? 0x0000ffffu : 0u) | (ok1 ? 0xffff0000u : 0u);
+                    }
+                }
+                mma_bf16(o[d0 / 8], a, b[0], b[1]);
+                mma_bf16(o[d0 / 8 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);                   // this warp is done with the stage
+    }
+    consumer_sync();
+    if (*abort_s) return;
+    // merge the four warps: (m, l, o) of each warp -> shared memory (all copies have landed and been used)
+    float* mo = reinterpret_cast<float*>(tiles);                // [4 warps][16 rows][HD]
+    float* mml = mo + 4 * 16 * HD;                              // [4][16][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+        if ((lane & 3) == 0) {
+            mml[(warp * 16 + row) * 2] = m[r];
+            mml[(warp * 16 + row) * 2 + 1] = l[r];
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            const int d = i * 8 + (lane & 3) * 2;
+            mo[(warp * 16 + row) * HD + d] = o[i][2 * r];
+            mo[(warp * 16 + row) * HD + d + 1] = o[i][2 * r + 1];
+        }
+    }
+    consumer_sync();
+    const float LN2 = 0.6931471805599453f;
+    for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
+        const int row = idx / HD, d = idx - row * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = mml[(w * 16 + row) * 2];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - M);
+                L += mml[(w * 16 + row) * 2 + 1] * f;
+                acc += mo[(w * 16 + row) * HD + d] * f;
+            }
+        }
+        const int h = kh * g + row;
+        if (n_splits == 1) {
+            out[((size_t)t * nh + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else {
+            const size_t slot = ((size_t)t * nh + h) * n_splits + sp;
+            part_o[slot * HD + d] = acc;
+            if (d == 0) {
+                part_ml[slot * 2] = M == -INFINITY ? -INFINITY : M * LN2;   // natural-log units for the combine kernel
+                part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult st;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &st) == cudaSuccess &&
+            st == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Fills `map_out` (128 bytes, 64-byte aligned host memory) with a tensor map over the cache pages of
+// one layer: a [rows, hd] bfloat16 matrix (rows = pages * kv_heads * page_size) read in boxes of
+// [page_size rows, hd elements] (one page of one head) with the 128-byte swizzle.  Returns 0, or PICO_ERR_SIZE for sizes
+// the TMA kernels do not take, or -7 when the driver refuses.
+PICO_API int pico_make_kv_tensor_map(void* map_out, const void* base, long long rows, int hd, int page_size) {
+    if (hd % 64 != 0 || hd < 64 || hd > 256 || page_size < 8 || page_size > MMA_BN || MMA_BN % page_size != 0 ||
+        (page_size & 7) != 0 || ((uintptr_t)base & 15) != 0)
+        return PICO_ERR_SIZE;
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return -7;
+    // dimensions: 64 elements of a 128-byte segment, the hd/64 segments of a row, the rows; one box is a
+    // whole page of one key/value head
+    const cuuint64_t dims[3] = {64, (cuuint64_t)(hd / 64), (cuuint64_t)rows};
+    const cuuint64_t strides[2] = {128, (cuuint64_t)hd * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)(hd / 64), (cuuint32_t)page_size};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          TMA_L2_PROMO, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -7;
+}
+
+__global__ void decode_combine_kernel(const float*, const float*, bf16*, const int*, int, int, int);
+int pico_launch_decode_combine(const float* part_o, const float* part_ml, void* out, const int* tok_list, int n_tok,
+                               int nh, int hd, int n_splits, cudaStream_t stream);
+
+// Single tokens with TMA-fed tiles.  k_map / v_map: tensor maps made by pico_make_kv_tensor_map (host
+// pointers; they are copied into the kernel's parameters).  Other arguments as pico_paged_decode_mma.
+PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const void* q, int q_row_stride, void* out,
+                                   float* part_o, float* part_ml, const int* tok_list, int n_tok, const int* tok_seg,
+                                   const int* positions, const int* block_table, int table_stride, int nh, int nkv,
+                                   int hd, int page_size, int window, float scale, int n_splits,
+                                   cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
+    const int g = nh / nkv;
+    if (g > 16 || nkv > 65535 || n_tok > 65535 || n_splits < 1 || n_splits > 64) return PICO_ERR_SIZE;
+    if (page_size < 8 || MMA_BN % page_size != 0) return PICO_ERR_SIZE;
+    if (n_splits > 1 && (!part_o || !part_ml)) return PICO_ERR_SIZE;
+    if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
+    const dim3 grid(n_splits, nkv, n_tok);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = (size_t)TMA_STAGES * 2 * MMA_BN * hd * 2 + (size_t)16 * (hd + 8) * 2 + 2 * TMA_STAGES * 8 + 8 +
+                        TMA_TABLE_CACHE * 4 + 1024;
+    CUtensorMap km, vm;
+    memcpy(&km, k_map, sizeof(CUtensorMap));
+    memcpy(&vm, v_map, sizeof(CUtensorMap));
+#define LAUNCH_TMA(HD)                                                                                              \
+    do {                                                                                                            \
+        cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        pico_launch((paged_decode_tma_kernel<HD>), dim3(grid), dim3(TMA_THREADS), smem, stream,                                            \
+            km, vm, (const bf16*)q, q_row_stride, (bf16*)out, part_o, part_ml, tok_list, tok_seg, positions,        \
+            block_table, table_stride, nh, nkv, page_size, window, scale_log2, n_splits);                           \
+    } while (0)
+    if (hd == 64) LAUNCH_TMA(64);
+    else LAUNCH_TMA(128);
+#undef LAUNCH_TMA
+    if (n_splits > 1) return pico_launch_decode_combine(part_o, part_ml, out, tok_list, n_tok, nh, hd, n_splits, stream);
+    return pico_launch_status();
+}

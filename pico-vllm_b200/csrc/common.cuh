@@ -66,3 +66,28 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int pico_launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch: every kernel of this library is launched with the attribute that
+// lets it start while the kernel before it in the stream is still draining, and therefore begins
+// with pdl_launch_dependents() (the next kernel may be scheduled) and calls pdl_wait() before it
+// touches anything an earlier kernel wrote (pdl_wait returns when the earlier grids have completed
+// and their writes are visible).  What a kernel does before pdl_wait - setting up barriers,
+// prefetching weights - overlaps the earlier kernel's tail.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline void pico_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

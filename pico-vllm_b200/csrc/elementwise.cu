@@ -11,6 +11,8 @@
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x;
     const int id = ids[row];
     const bool ok = id >= 0 && id < V;
@@ -24,9 +26,9 @@ PICO_API int pico_embedding(const int* ids, const void* table, int table_dtype, 
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == PICO_F32)
-        embedding_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
+        pico_launch((embedding_kernel<float>), dim3(T), dim3(threads), 0, stream, ids, (const float*)table, out, H, V);
     else if (table_dtype == PICO_BF16)
-        embedding_kernel<bf16><<<T, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V);
+        pico_launch((embedding_kernel<bf16>), dim3(T), dim3(threads), 0, stream, ids, (const bf16*)table, out, H, V);
     else
         return PICO_ERR_DTYPE;
     return pico_launch_status();
@@ -41,6 +43,8 @@ template <typename TA>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta,
                                    const float* __restrict__ weight, TA* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float vals[];  // H floats, then 33 of scratch
     float* scratch = vals + H;
     const int r = blockIdx.x;
@@ -73,11 +77,11 @@ PICO_API int pico_add_rmsnorm(float* x, const void* delta, const float* weight, 
     if (act_dtype == PICO_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<R, threads, smem, stream>>>(x, (const float*)delta, weight, (float*)out, rows, H, eps);
+        pico_launch((add_rmsnorm_kernel<float>), dim3(R), dim3(threads), smem, stream, x, (const float*)delta, weight, (float*)out, rows, H, eps);
     } else if (act_dtype == PICO_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<bf16><<<R, threads, smem, stream>>>(x, (const bf16*)delta, weight, (bf16*)out, rows, H, eps);
+        pico_launch((add_rmsnorm_kernel<bf16>), dim3(R), dim3(threads), smem, stream, x, (const bf16*)delta, weight, (bf16*)out, rows, H, eps);
     } else
         return PICO_ERR_DTYPE;
     return pico_launch_status();
@@ -87,6 +91,8 @@ PICO_API int pico_add_rmsnorm(float* x, const void* delta, const float* weight, 
 // gate_up: [T, 2*I] with the gate columns first; out[t, i] = silu(gate) * up.
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, int I, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
@@ -105,9 +111,9 @@ PICO_API int pico_swiglu(const void* gate_up, void* out, int T, int I, int act_d
     size_t want = (total + threads - 1) / threads;
     const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
     if (act_dtype == PICO_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+        pico_launch((swiglu_kernel<float>), dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total);
     else if (act_dtype == PICO_BF16)
-        swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+        pico_launch((swiglu_kernel<bf16>), dim3(blocks), dim3(threads), 0, stream, (const bf16*)gate_up, (bf16*)out, I, total);
     else
         return PICO_ERR_DTYPE;
     return pico_launch_status();

@@ -1,0 +1,72 @@
+// Tensor-core building blocks shared by the attention kernels: cp.async, ldmatrix and
+// mma.sync m16n8k16 (bf16 in, float32 accumulate) wrappers.
+#pragma once
+#include "common.cuh"
+
+#define MMA_BN 64          // cache positions per shared-memory tile
+#define MMA_THREADS 128    // 4 warps
+#define DEC_STAGES 3       // tiles in flight in the decode kernel
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool pred) {
+    const int n = pred ? 16 : 0;   // src-size 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+
+// Running softmax over one tile of scores for the two rows a thread holds (lane/4 and lane/4+8).
+// s: scores already scaled to log2 units and masked with -inf.  On return s holds p = 2^(s - m).
+template <int HD_MAX, int NT>
+__device__ __forceinline__ void online_softmax(float (&s)[NT][4], float (&m)[2], float (&l)[2],
+                                               float (&o)[HD_MAX / 8][4]) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) mx = fmaxf(mx, fmaxf(s[j][2 * r], s[j][2 * r + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m[r], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
+        const float corr = exp2f(m[r] - m_use);                      // m = -inf gives 0
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const float p0 = exp2f(s[j][2 * r] - m_use), p1 = exp2f(s[j][2 * r + 1] - m_use);
+            s[j][2 * r] = p0;
+            s[j][2 * r + 1] = p1;
+            sum += p0 + p1;
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l[r] = l[r] * corr + sum;
+        m[r] = m_new;
+#pragma unroll
+        for (int i = 0; i < HD_MAX / 8; ++i) {
+            o[i][2 * r] *= corr;
+            o[i][2 * r + 1] *= corr;
+        }
+    }
+}
+

@@ -17,6 +17,8 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const fl
                                   const int* __restrict__ slots, TA* __restrict__ k_pages,
                                   TA* __restrict__ v_pages, int nh, int nkv, int hd, int rot_half,
                                   int page_size) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float cs[];  // cos[rot_half], sin[rot_half]
     const int t = blockIdx.x;
     const float pos = (float)positions[t];
@@ -79,11 +81,11 @@ PICO_API int pico_rope_store(void* qkv, int row_stride, const float* bias, const
     const int work = (nh + nkv) * (hd / 2);
     const int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
     if (act_dtype == PICO_F32)
-        rope_store_kernel<float><<<T, threads, smem, stream>>>((float*)qkv, row_stride, bias, positions, inv_freq,
+        pico_launch((rope_store_kernel<float>), dim3(T), dim3(threads), smem, stream, (float*)qkv, row_stride, bias, positions, inv_freq,
                                                                slots, (float*)k_pages, (float*)v_pages, nh, nkv, hd,
                                                                rot_half, page_size);
     else if (act_dtype == PICO_BF16)
-        rope_store_kernel<bf16><<<T, threads, smem, stream>>>((bf16*)qkv, row_stride, bias, positions, inv_freq,
+        pico_launch((rope_store_kernel<bf16>), dim3(T), dim3(threads), smem, stream, (bf16*)qkv, row_stride, bias, positions, inv_freq,
                                                               slots, (bf16*)k_pages, (bf16*)v_pages, nh, nkv, hd,
                                                               rot_half, page_size);
     else

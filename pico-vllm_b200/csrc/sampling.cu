@@ -49,6 +49,8 @@ __device__ __forceinline__ float block_excl_scan(float v, float* scratch, float*
 __global__ void sample_kernel(const float* __restrict__ logits, int row_stride, int V,
                               const float* __restrict__ temperature, const float* __restrict__ top_p,
                               const float* __restrict__ uniform, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     __shared__ int iscratch[33];
     const int r = blockIdx.x;
@@ -161,12 +163,14 @@ PICO_API int pico_sample(const float* logits, int row_stride, int R, int V, cons
     if (R <= 0) return 0;
     if (V <= 0) return PICO_ERR_SIZE;
     if (temperature && !uniform) return PICO_ERR_SIZE;
-    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_p, uniform, out);
+    pico_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, V, temperature, top_p, uniform, out);
     return pico_launch_status();
 }
 
 // float32 copy of bfloat16 rows (logits of the bfloat16 path are handed out as float32)
 __global__ void bf16_to_f32_kernel(const bf16* __restrict__ in, float* __restrict__ out, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = __bfloat162float(in[i]);
 }
@@ -174,6 +178,6 @@ PICO_API int pico_bf16_to_f32(const void* in, float* out, long long n, cudaStrea
     if (n <= 0) return 0;
     long long want = (n + 255) / 256;
     const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
-    bf16_to_f32_kernel<<<blocks, 256, 0, stream>>>((const bf16*)in, out, (size_t)n);
+    pico_launch(bf16_to_f32_kernel, dim3(blocks), dim3(256), 0, stream, (const bf16*)in, out, (size_t)n);
     return pico_launch_status();
 }

@@ -199,6 +199,7 @@ __device__ __forceinline__ void sg_epilogue(const SkinnyArgs& p, const float* re
 // for every tile); otherwise each warp streams its slices of them beside the weights.
 template <int MT, int EPI, int STAGES, bool XPRE>     // MT: tokens padded to 8 * MT
 __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArgs p, int n_tiles, int x_ld) {
+    pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char sg_smem[];
     constexpr int XR = MT * 8;                               // token rows
     constexpr int STAGE_ROWS = XPRE ? 16 : 16 + XR;
@@ -241,6 +242,14 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
     };
 
     if (XPRE) {
+        // the weights do not depend on the kernel before this one: their stream starts at once,
+        // and only then does the block wait for that kernel's output, the activations
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < total) load_step(s);
+            sg_commit();
+        }
+        pdl_wait();
         const int chunks = (nk64 * SG_KW) >> 3;                  // per row, K rounded up to 64
         for (int idx = threadIdx.x; idx < XR * chunks; idx += SG_THREADS) {
             const int r = idx / chunks, c = idx - r * chunks;
@@ -248,15 +257,16 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
             const bool ok = k < p.K && r < p.M;
             sg_cp16(sg_smem_u32(x_all + r * x_ld + k), p.x + (size_t)(ok ? r : 0) * p.ldx + (ok ? k : 0), ok);
         }
-    }
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < total) load_step(s);
         sg_commit();
-    }
-    if (XPRE) {
         sg_wait<0>();            // once per block: the activations (and the first weight stages) have landed
         __syncthreads();
+    } else {
+        pdl_wait();
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < total) load_step(s);
+            sg_commit();
+        }
     }
     float acc[MT][4];
 #pragma unroll
@@ -322,7 +332,7 @@ static void sg_launch_one(const SkinnyArgs& a, int tiles, int grid, cudaStream_t
     const size_t smem = (size_t)SG_WARPS * STAGES * (XPRE ? 16 : 16 + MT * 8) * SG_LD * sizeof(bf16) +
                         (XPRE ? (size_t)MT * 8 * x_ld * sizeof(bf16) : 0) + (size_t)SG_WARPS * 16 * MT * 8 * sizeof(float);
     cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI, STAGES, XPRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    skinny_gemm_kernel<MT, EPI, STAGES, XPRE><<<grid, SG_THREADS, smem, stream>>>(a, tiles, x_ld);
+    pico_launch((skinny_gemm_kernel<MT, EPI, STAGES, XPRE>), dim3(grid), dim3(SG_THREADS), smem, stream, a, tiles, x_ld);
 }
 
 template <int EPI>

@@ -59,6 +59,10 @@ def library():
         "pico_skinny_linear_residual": [vp, i32, vp, vp, i32, i32, i32, vp],
         "pico_skinny_gate_up_swiglu": [vp, i32, vp, vp, i32, i32, i32, vp],
         "pico_skinny_qkv_rope_store": [vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+        "pico_make_kv_tensor_map": [vp, vp, i64, i32, i32],
+        "pico_paged_decode_tma": [vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+                                  f32, i32, vp],
+        "pico_tma_status": [vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_bf16_to_f32": [vp, vp, i64, vp],
     }
@@ -241,17 +245,45 @@ def mma_attention_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_
             and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 16)
 
 
+def make_kv_tensor_map(pages: torch.Tensor):
+    """A TMA tensor map over the cache pages of one layer ([pages, kv_heads, page_size, head_dim]
+    bfloat16, contiguous), for the TMA-fed decode kernel; None when the sizes are not taken (head_dim
+    64 or 128, page size 8, 16, 32 or 64).  The returned object must be kept alive while it is used."""
+    if not pages.is_cuda or pages.dtype != torch.bfloat16 or not pages.is_contiguous() or pages.dim() != 4:
+        return None
+    n_pages, nkv, ps, hd = pages.shape
+    if hd not in (64, 128) or ps not in (8, 16, 32, 64):
+        return None
+    buf = (ctypes.c_ubyte * 192)()
+    addr = ctypes.addressof(buf)
+    aligned = (addr + 63) & ~63                      # a tensor map is 128 bytes on a 64-byte boundary
+    rc = library().pico_make_kv_tensor_map(aligned, pages.data_ptr(), n_pages * nkv * ps, hd, ps)
+    if rc != 0:
+        return None
+    return (buf, aligned)
+
+
+def tma_status() -> int:
+    """0, or 1 when a kernel gave up waiting for a TMA copy since the library was loaded."""
+    out = ctypes.c_int(0)
+    library().pico_tma_status(ctypes.addressof(out))
+    return out.value
+
+
 def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                         tok_seg: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                         cu_q: torch.Tensor, prefill_segs: Optional[torch.Tensor], n_prefill_segs: int,
                         max_prefill_q: int, decode_tokens: Optional[torch.Tensor], n_decode_tokens: int,
                         n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
-                        scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
+                        k_map=None, v_map=None) -> torch.Tensor:
     """The same attention as :func:`paged_attention` for bfloat16 on tensor cores, in two launches:
     segments that bring two or more tokens (``prefill_segs`` int32 [n_prefill_segs], None = all
     segments; ``cu_q`` int32 [segments + 1]; ``max_prefill_q`` their longest) and single tokens
     (``decode_tokens`` int32 [n_decode_tokens], None = every token of the batch) whose key range is
-    cut into ``n_splits`` parts.  Every token of the batch must be in exactly one of the two."""
+    cut into ``n_splits`` parts.  Every token of the batch must be in exactly one of the two.
+    With ``k_map`` / ``v_map`` (from :func:`make_kv_tensor_map` over these same pages) the single
+    tokens run in the kernel that brings pages in by TMA."""
     _cuda(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs, decode_tokens, scratch)
     T = q.shape[0]
     if not mma_attention_takes(q.dtype, n_heads, n_kv_heads, head_dim):
@@ -285,11 +317,19 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                 raise KernelError(f"paged_attention_mma: n_splits={n_splits} needs {need} float32 of scratch")
             part_o = scratch.data_ptr()
             part_ml = part_o + 4 * T * n_heads * n_splits * head_dim
-        _check(lib.pico_paged_decode_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o,
-                                         part_ml, _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg),
-                                         _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
-                                         n_kv_heads, head_dim, page_size, win, float(scale), n_splits, _stream()),
-               f"paged_decode_mma (head_dim {head_dim})")
+        if k_map is not None and v_map is not None:
+            _check(lib.pico_paged_decode_tma(k_map[1], v_map[1], _ptr(q), q.stride(0), _ptr(out), part_o, part_ml,
+                                             _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg), _ptr(positions),
+                                             _ptr(block_table), block_table.stride(0), n_heads, n_kv_heads,
+                                             head_dim, page_size, win, float(scale), n_splits, _stream()),
+                   f"paged_decode_tma (head_dim {head_dim})")
+        else:
+            _check(lib.pico_paged_decode_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), part_o,
+                                             part_ml, _ptr(decode_tokens), n_decode_tokens, _ptr(tok_seg),
+                                             _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
+                                             n_kv_heads, head_dim, page_size, win, float(scale), n_splits,
+                                             _stream()),
+                   f"paged_decode_mma (head_dim {head_dim})")
         _count(2 if n_splits > 1 else 1)
     return out
 

@@ -75,6 +75,8 @@ class CacheView:
     page_size: int = 0
     store: bool = True
     state: Optional[torch.Tensor] = None
+    k_map: object = None       # TMA tensor maps over k and v (ops.make_kv_tensor_map), or None
+    v_map: object = None
 
 
 class Part:

@@ -101,7 +101,7 @@ def mma_attention_takes(dtype, n_heads, n_kv_heads, head_dim):
 
 def paged_attention_mma(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs,
                         n_prefill_segs, max_prefill_q, decode_tokens, n_decode_tokens, n_heads, n_kv_heads, head_dim,
-                        page_size, window, scale, n_splits=1, scratch=None):
+                        page_size, window, scale, n_splits=1, scratch=None, k_map=None, v_map=None):
     return paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads, head_dim,
                            page_size, window, scale)
 
@@ -139,6 +139,10 @@ def skinny_qkv_rope_store(x, qkv_weight, bias, positions, inv_freq, slots, k_pag
     return qkv[:, :n_heads * head_dim].to(torch.bfloat16)
 
 
+def make_kv_tensor_map(pages):
+    return None
+
+
 def linear(x, weight, out=None):
     y = (x.float() @ weight.float().t()).to(x.dtype)
     if out is not None:
@@ -170,7 +174,7 @@ def sample(logits, temperature, top_p, uniform, out):
 
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
-         "mma_attention_takes", "paged_attention_mma", "skinny_takes", "skinny_linear", "skinny_linear_residual",
+         "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "skinny_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
          "linear", "logits_linear", "sample"]
 

@@ -98,7 +98,8 @@ def test_rope_store(dtype, nh, nkv, hd, ps, rot):
     assert torch.allclose(qg2.cpu().float()[:, :nh * hd], qr.float()[:, :nh * hd], **t)
 
 
-def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, seed=0, spike=False, mma=False):
+def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, seed=0, spike=False, mma=False,
+                    tma=False, poison=False):
     """Segments with kv lengths seg_lens, of which the last q_lens are this step's queries."""
     from pico_vllm_b200 import ops
     g = gen(20 + seed)
@@ -138,9 +139,25 @@ def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, se
         pf = torch.tensor([i for i, n in enumerate(q_lens) if n > 1], dtype=torch.int32)
         dec = torch.tensor([int(cu[i]) for i, n in enumerate(q_lens) if n == 1], dtype=torch.int32)
         out.fill_(float("nan"))
-        ops.paged_attention_mma(q.to(DEV), k.to(DEV), v.to(DEV), out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
+        kd, vd = k.to(DEV), v.to(DEV)
+        if poison:
+            # what lies beyond a request's last token inside its last page, and pages it does not hold,
+            # is not-a-number: nothing of it may reach the result
+            held = torch.zeros(pages, ps, dtype=torch.bool)
+            for sgi, L in enumerate(seg_lens):
+                for n in range(L):
+                    held[table[sgi, n // ps], n % ps] = True
+            kd[~held.to(DEV)[:, None, :].expand(-1, nkv, -1)] = float("nan")
+            vd[~held.to(DEV)[:, None, :].expand(-1, nkv, -1)] = float("nan")
+        maps = (ops.make_kv_tensor_map(kd), ops.make_kv_tensor_map(vd)) if tma else (None, None)
+        if tma:
+            assert maps[0] is not None and maps[1] is not None
+        ops.paged_attention_mma(q.to(DEV), kd, vd, out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
                                 cu.to(DEV), pf.to(DEV), len(pf), max([n for n in q_lens if n > 1], default=0),
-                                dec.to(DEV), len(dec), nh, nkv, hd, ps, window, scale, splits, scratch)
+                                dec.to(DEV), len(dec), nh, nkv, hd, ps, window, scale, splits, scratch, *maps)
+        if tma:
+            torch.cuda.synchronize()
+            assert ops.tma_status() == 0
     else:
         ops.paged_attention(q.to(DEV), k.to(DEV), v.to(DEV), out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
                             nh, nkv, hd, ps, window, scale, splits, scratch)
@@ -198,6 +215,23 @@ def test_mma_decode_split_keys(splits, window, nh, nkv, hd):
     got, want = _attention_case(torch.bfloat16, nh, nkv, hd, 16, window, seg_lens=[700, 333, 40, 3, 64, 65, 1],
                                 q_lens=[1, 1, 1, 1, 1, 1, 1], splits=splits, seed=3, mma=True)
     assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("window", [None, 100, 37])
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(6, 2, 64, 16), (12, 2, 128, 16), (7, 1, 128, 8), (16, 1, 64, 32), (4, 4, 128, 64)])
+def test_tma_decode_split_keys(splits, window, nh, nkv, hd, ps):
+    got, want = _attention_case(torch.bfloat16, nh, nkv, hd, ps, window, seg_lens=[700, 333, 40, 3, 64, 65, 1, 128],
+                                q_lens=[1, 1, 1, 1, 1, 1, 1, 1], splits=splits, seed=3, mma=True, tma=True, poison=True)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("window,splits", [(None, 1), (None, 8), (64, 1), (64, 4)])
+def test_tma_decode_far_key_and_window_edge(window, splits):
+    got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=[1, 1], splits=splits,
+                                seed=5, spike=True, mma=True, tma=True, poison=True)
     assert torch.allclose(got, want, **MMA_TOL)
 
 
