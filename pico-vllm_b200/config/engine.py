@@ -34,6 +34,7 @@ class EngineConfig:
     max_model_len: Optional[int] = None  # longest request; None = max_position_embeddings
     use_cuda_graph: bool = True        # replay decode-only steps from a CUDA graph (pico_vllm/engine.py:98-137)
     graph_batch_sizes: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
+    async_scheduling: bool = True      # launch a step before the tokens of the step before are read
     seed: int = 0
     device: str = "cuda:0"
 

@@ -8,13 +8,17 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
+// An id below zero stands for "the token chosen in the step before": id = -(j + 1) takes
+// feedback[j], the j-th token the sampling kernel wrote, so that a step can be launched before the
+// host has read the last step's tokens.
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
-                                 float* __restrict__ out, int H, int V) {
+                                 float* __restrict__ out, int H, int V, const int* __restrict__ feedback) {
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x;
-    const int id = ids[row];
+    int id = ids[row];
+    if (id < 0 && feedback) id = feedback[-id - 1];
     const bool ok = id >= 0 && id < V;
     const TW* src = table + (size_t)(ok ? id : 0) * H;
     float* dst = out + (size_t)row * H;
@@ -22,13 +26,13 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restri
 }
 
 PICO_API int pico_embedding(const int* ids, const void* table, int table_dtype, float* out, int T, int H,
-                            int V, cudaStream_t stream) {
+                            int V, const int* feedback, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == PICO_F32)
-        pico_launch((embedding_kernel<float>), dim3(T), dim3(threads), 0, stream, ids, (const float*)table, out, H, V);
+        pico_launch((embedding_kernel<float>), dim3(T), dim3(threads), 0, stream, ids, (const float*)table, out, H, V, feedback);
     else if (table_dtype == PICO_BF16)
-        pico_launch((embedding_kernel<bf16>), dim3(T), dim3(threads), 0, stream, ids, (const bf16*)table, out, H, V);
+        pico_launch((embedding_kernel<bf16>), dim3(T), dim3(threads), 0, stream, ids, (const bf16*)table, out, H, V, feedback);
     else
         return PICO_ERR_DTYPE;
     return pico_launch_status();

@@ -43,3 +43,5 @@ class Batch:
     max_prefill_q: int = 0
     decode_tokens: Optional[torch.Tensor] = None  # int32: tokens of one-token segments (None: every token)
     num_decode_tokens: int = 0
+    # tokens chosen by the sampling kernel in the step before; a token id -(j+1) in token_ids means feedback[j]
+    feedback: Optional[torch.Tensor] = None

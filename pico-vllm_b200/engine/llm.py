@@ -62,6 +62,7 @@ class LLM:
                                    self.cfg.prefill_chunk, eos)
         self._next_id = 0
         self._no_more = False
+        self._pending = None            # (plan, tokens on their way) of the step launched last
         self.requests: Dict[int, Request] = {}
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0}
 
@@ -86,7 +87,7 @@ class LLM:
         self._no_more = True
 
     def is_done(self) -> bool:
-        return self._no_more and not self.scheduler.has_work()
+        return self._no_more and not self.scheduler.has_work() and self._pending is None
 
     def step(self) -> List[Tuple[int, Union[str, List[int]]]]:
         """One batch: schedule, run, sample, finish.  Returns (id, prompt + generated) of the
@@ -112,6 +113,8 @@ class LLM:
         while pending:
             for r in self._step():
                 pending.discard(r.request_id)
+        while self._pending is not None:        # a last step may still be in flight (its tokens are dropped)
+            self._step()
         self._no_more = was
         outs = []
         for rid in ids:
@@ -123,24 +126,50 @@ class LLM:
 
     # ------------------------------------------------------------------ inside
     def _step(self) -> List[Request]:
+        if self.cfg.async_scheduling:
+            return self._step_ahead()
         plan = self.scheduler.schedule()
         if not plan:
             return []
+        logits, rows = self._launch(plan)
+        toks = self.sampler.sample(logits, *self._sampling_args(rows))
+        it = iter(toks)
+        sampled = [next(it) if s.samples else None for s in plan]
+        self.stats["steps"] += 1
+        return self.scheduler.finish_step(plan, sampled)
+
+    def _step_ahead(self) -> List[Request]:
+        """One step ahead of the device: the next batch is scheduled, built and launched while the
+        tokens of the batch before are still being computed; the embedding takes them from where
+        the sampling kernel left them.  The tokens are read (and requests finished) one step late."""
+        plan = self.scheduler.schedule() if (self.scheduler.waiting or self.scheduler.running) else []
+        launched = None
+        if plan:
+            logits, rows = self._launch(plan)
+            handle = self.sampler.sample_async(logits, *self._sampling_args(rows), out=self.runner.feedback)
+            self.scheduler.advance(plan)
+            launched = (plan, handle)
+            self.stats["steps"] += 1
+        done: List[Request] = []
+        if self._pending is not None:
+            prev_plan, prev_handle = self._pending
+            done = self.scheduler.resolve(prev_plan, prev_handle.result())
+        self._pending = launched
+        return done
+
+    def _launch(self, plan):
         items = []
         for s in plan:
             toks = s.request.all_ids[s.start:s.start + s.count]
             items.append(StepItem(s.request.slot, toks, (s.count - 1,) if s.samples else ()))
             self.stats["decode_tokens" if s.request.is_decoding else "prefill_tokens"] += s.count
         logits = self.runner.step(items)
-        rows = [s for s in plan if s.samples]
+        return logits, [s for s in plan if s.samples]
+
+    def _sampling_args(self, rows):
         seeds = [(r.request.seed if r.request.seed is not None else self.cfg.seed) for r in rows]
-        toks = self.sampler.sample(
-            logits, [r.request.temperature for r in rows], [r.request.top_p for r in rows],
-            [uniform_for(sd, r.request.request_id, len(r.request.generated_ids)) for sd, r in zip(seeds, rows)])
-        it = iter(toks)
-        sampled = [next(it) if s.samples else None for s in plan]
-        self.stats["steps"] += 1
-        return self.scheduler.finish_step(plan, sampled)
+        return ([r.request.temperature for r in rows], [r.request.top_p for r in rows],
+                [uniform_for(sd, r.request.request_id, len(r.request.generated_ids)) for sd, r in zip(seeds, rows)])
 
     def _encode(self, prompt: Prompt) -> List[int]:
         if isinstance(prompt, str):

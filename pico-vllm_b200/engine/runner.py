@@ -88,6 +88,9 @@ class ModelRunner:
         self._stage: Optional[_Staging] = None
         self.graph_replays = 0
         self.steps = 0
+        # where the sampling kernel leaves the tokens of a step for the next step's embedding
+        self.feedback = torch.zeros(max(64, cache.max_num_seqs, max(cfg.graph_batch_sizes)), dtype=torch.int32,
+                                    device=self.device)
         kv = [g.spec for g in cache.groups]
         self._max_heads = 0
         for blk in model.blocks:
@@ -136,7 +139,7 @@ class ModelRunner:
             if it.slot in seen:
                 raise PicoError(f"slot {it.slot} appears twice in one step")
             seen.add(it.slot)
-            if min(it.tokens) < 0 or max(it.tokens) >= V:
+            if min(it.tokens) < -self.feedback.shape[0] or max(it.tokens) >= V:
                 raise PicoError(f"token id outside [0, {V}) in a step item")
             for w in it.want:
                 if not 0 <= w < len(it.tokens):
@@ -256,7 +259,7 @@ class ModelRunner:
                      prefill_segs=d(lay.prefill_segs, len(pf)) if len(pf) < S else None, num_prefill_segs=len(pf),
                      max_prefill_q=max([q_lens[i] for i in pf], default=0),
                      decode_tokens=d(lay.decode_tokens, len(dec)) if len(dec) < T else None,
-                     num_decode_tokens=len(dec))
+                     num_decode_tokens=len(dec), feedback=self.feedback)
 
     # ------------------------------------------------------------------ CUDA graph replay of decode steps
     def _bucket(self, n: int) -> int:

@@ -88,6 +88,7 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []       # in order of admission: oldest first
         self.finished: List[Request] = []
+        self.draining: List[Request] = []      # their last token is being computed; not scheduled again
         self.num_preemptions = 0
 
     # ------------------------------------------------------------------ requests in and out
@@ -104,7 +105,7 @@ class Scheduler:
         self.waiting.append(request)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self.draining)
 
     def _preempt(self, request: Request) -> None:
         self.cache.release(request.slot)
@@ -197,6 +198,70 @@ class Scheduler:
             self.running.append(req)
             take(req, n)
         return plan
+
+    # ------------------------------------------------------------------ one step ahead
+    # The engine may launch step k+1 before it has read the tokens of step k.  ``advance`` books a
+    # launched step without the token values (a placeholder stands for each token to come: -(j+1)
+    # for the j-th sampled row, which is what the next step's embedding reads on the device);
+    # ``resolve`` puts the values in when they arrive and finishes requests.  A request that ends by
+    # its token count is known at ``advance`` and is not scheduled again; one that ends by its end
+    # token has by then been launched once more: that work is thrown away, and its pages and slot are
+    # given back only when ``resolve`` is called for that later step (``release_when_idle``).
+    def advance(self, plan: Sequence[Scheduled]) -> None:
+        j = 0
+        for s in plan:
+            req = s.request
+            req.num_computed += s.count
+            if not s.samples:
+                continue
+            req.generated_ids.append(-(j + 1))
+            j += 1
+            req.in_flight = getattr(req, "in_flight", 0) + 1
+            if len(req.generated_ids) >= req.max_new_tokens or req.total_len >= self.cache.max_seq_len:
+                # the last token is on its way: nothing more to compute for this request
+                req.finish_reason = "length" if len(req.generated_ids) >= req.max_new_tokens else "cache_length"
+                if req in self.running:
+                    self.running.remove(req)
+                    self.draining.append(req)
+
+    def resolve(self, plan: Sequence[Scheduled], tokens: Sequence[int]) -> List[Request]:
+        """Token values of a step booked with ``advance``.  Returns the requests that finished."""
+        done: List[Request] = []
+        it = iter(tokens)
+        for j, s in enumerate(p for p in plan if p.samples):
+            req, tok = s.request, int(next(it))
+            req.in_flight -= 1
+            if req.status is RequestStatus.FINISHED:
+                # ended by its end token one step earlier; this step's token is dropped
+                if req.in_flight == 0 and req.slot is not None:
+                    self.cache.release(req.slot)
+                    req.slot = None
+                continue
+            # the oldest placeholder of this request is this step's token
+            at = next(i for i, t in enumerate(req.generated_ids) if t < 0)
+            req.generated_ids[at] = tok
+            hit_eos = not req.ignore_eos and self.eos_token_id is not None and tok == self.eos_token_id
+            last = at == len(req.generated_ids) - 1
+            if hit_eos or (last and req in self.draining):
+                if hit_eos:
+                    req.finish_reason = "eos"
+                    dropped = len(req.generated_ids) - at - 1        # tokens launched after the end token
+                    del req.generated_ids[at + 1:]
+                    req.num_computed = min(req.num_computed, req.total_len)
+                    _ = dropped
+                req.status = RequestStatus.FINISHED
+                if req in self.running:
+                    self.running.remove(req)
+                if req in self.draining:
+                    self.draining.remove(req)
+                if req in self.waiting:
+                    self.waiting.remove(req)
+                if req.in_flight == 0 and req.slot is not None:
+                    self.cache.release(req.slot)
+                    req.slot = None
+                self.finished.append(req)
+                done.append(req)
+        return done
 
     # ------------------------------------------------------------------ after the step
     def finish_step(self, plan: Sequence[Scheduled], sampled: Sequence[Optional[int]]) -> List[Request]:

@@ -84,7 +84,7 @@ class DecoderModel:
     def forward(self, batch, views: Sequence[CacheView]) -> torch.Tensor:
         """Runs the batch's tokens through every call of the order; returns float32 logits
         [len(batch.logit_rows), vocab]."""
-        x = self.embed.forward(batch.token_ids)
+        x = self.embed.forward(batch.token_ids, batch.feedback)
         pending = None
         for call in self.order:
             view = None

@@ -46,7 +46,7 @@ def library():
         raise KernelError(f"cannot load the kernel library {path}: {e}") from None
     vp, i32, f32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
     sigs = {
-        "pico_embedding": [vp, vp, i32, vp, i32, i32, i32, vp],
+        "pico_embedding": [vp, vp, i32, vp, i32, i32, i32, vp, vp],
         "pico_add_rmsnorm": [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
         "pico_swiglu": [vp, vp, i32, i32, i32, vp],
         "pico_rope_store": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
@@ -104,16 +104,21 @@ def _count(n: int = 1) -> None:
 
 
 # ------------------------------------------------------------------------------------------
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = float32(table[ids[t], :]).  ids int32 [T]; table [V, H]; out float32 [T, H]."""
-    _cuda(ids, table, out)
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+              feedback: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, :] = float32(table[ids[t], :]).  ids int32 [T]; table [V, H]; out float32 [T, H].
+    With ``feedback`` (int32), an id -(j+1) means feedback[j]: the token the sampling kernel chose
+    in the step before, which the host may not have read yet."""
+    _cuda(ids, table, out, feedback)
+    if feedback is not None and feedback.dtype != torch.int32:
+        raise KernelError("embedding: feedback must be int32")
     T, (V, H) = ids.shape[0], table.shape
     if ids.dtype != torch.int32 or out.dtype != torch.float32 or out.shape != (T, H):
         raise KernelError("embedding: ids must be int32 [T] and out float32 [T, H]")
     if not (table.is_contiguous() and out.is_contiguous() and ids.is_contiguous()):
         raise KernelError("embedding: tensors must be contiguous")
-    _check(library().pico_embedding(_ptr(ids), _ptr(table), _dtype_code(table), _ptr(out), T, H, V, _stream()),
-           "embedding")
+    _check(library().pico_embedding(_ptr(ids), _ptr(table), _dtype_code(table), _ptr(out), T, H, V, _ptr(feedback),
+                                    _stream()), "embedding")
     _count()
     return out
 

@@ -24,9 +24,9 @@ class TokenEmbedding(Part):
     def params(self) -> List[Param]:
         return [Param("weight", (Piece("weight", (self.vocab, self.width)),))]
 
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, ids: torch.Tensor, feedback: Optional[torch.Tensor] = None) -> torch.Tensor:
         out = torch.empty((ids.shape[0], self.width), dtype=torch.float32, device=ids.device)
-        return ops.embedding(ids, self.weight, out)
+        return ops.embedding(ids, self.weight, out, feedback)
 
 
 class OutputHead(Part):

@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import Sampler, uniform_for
+from .sampler import Sampler, PendingTokens, uniform_for
 
-__all__ = ["SamplingParams", "Sampler", "uniform_for"]
+__all__ = ["SamplingParams", "Sampler", "PendingTokens", "uniform_for"]

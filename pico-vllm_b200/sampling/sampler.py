@@ -31,10 +31,50 @@ def uniform_for(seed: int, request_id: int, step: int) -> float:
     return (h >> 40) / float(1 << 24)
 
 
+class PendingTokens:
+    """Tokens a sampling kernel is writing: ``result()`` waits for the copy to the host."""
+
+    def __init__(self, host: torch.Tensor, event, n: int):
+        self.host, self.event, self.n = host, event, n
+
+    def result(self) -> List[int]:
+        if self.event is not None:
+            self.event.synchronize()
+        return self.host[:self.n].tolist()
+
+
 class Sampler:
     def __init__(self, device, seed: int = 0):
         self.device = torch.device(device)
         self.seed = seed
+        self._host = [None, None]       # two pinned buffers, used in turn
+        self._turn = 0
+
+    def sample_async(self, logits: torch.Tensor, temperatures: Sequence[float], top_ps: Sequence[float],
+                     uniforms: Optional[Sequence[float]], out: torch.Tensor) -> PendingTokens:
+        """Like :meth:`sample`, but the tokens go to ``out`` (int32 on the device, at least R long)
+        and to the host without waiting: the returned object's ``result()`` waits."""
+        R = logits.shape[0]
+        cuda = self.device.type == "cuda"
+        if self._host[self._turn] is None or self._host[self._turn].numel() < max(R, 1):
+            self._host[self._turn] = torch.empty(max(64, R), dtype=torch.int32, pin_memory=cuda)
+        host = self._host[self._turn]
+        self._turn ^= 1
+        if R == 0:
+            return PendingTokens(host, None, 0)
+        dst = out[:R]
+        if all(t <= 0 for t in temperatures):
+            ops.sample(logits, None, None, None, dst)
+        else:
+            params = torch.tensor([list(temperatures), list(top_ps), list(uniforms)], dtype=torch.float32)
+            dev = params.to(self.device, non_blocking=True)
+            ops.sample(logits, dev[0], dev[1], dev[2], dst)
+        host[:R].copy_(dst, non_blocking=True)
+        event = None
+        if cuda:
+            event = torch.cuda.Event()
+            event.record()
+        return PendingTokens(host, event, R)
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], top_ps: Sequence[float],
                uniforms: Optional[Sequence[float]] = None) -> List[int]:

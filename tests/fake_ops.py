@@ -12,8 +12,11 @@ import torch
 import plain_qwen2 as plain
 
 
-def embedding(ids, table, out):
-    out.copy_(table[ids.long()].float())
+def embedding(ids, table, out, feedback=None):
+    ids = ids.long()
+    if feedback is not None:
+        ids = torch.where(ids < 0, feedback.long()[(-ids - 1).clamp(min=0)], ids)
+    out.copy_(table[ids].float())
     return out
 
 

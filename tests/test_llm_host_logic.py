@@ -14,9 +14,13 @@ def _llm(monkeypatch, tmp_path, name, **opts):
                page_size=helpers.TINY[name]["page_size"], **opts)
 
 
-def test_greedy_generation_equals_plain(monkeypatch, tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("ahead", [True, False])
+def test_greedy_generation_equals_plain(monkeypatch, tmp_path, ahead):
     from pico_vllm_b200 import SamplingParams
-    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=512)
+    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=512, async_scheduling=ahead)
     cfg = helpers.tiny_config("a")
     prompts = [helpers.random_ids(n, cfg.vocab_size, 7 + n) for n in (5, 17, 33)]
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=8, ignore_eos=True))
@@ -68,3 +72,25 @@ def test_sampled_tokens_do_not_depend_on_batching(monkeypatch, tmp_path):
     llm2 = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=512)
     alone = [llm2.generate([p], sp)[0] for p in prompts]
     assert [o.token_ids for o in together] == [o.token_ids for o in alone]
+
+
+@pytest.mark.parametrize("ahead", [True, False])
+def test_end_token_stops_a_request_and_frees_its_pages(monkeypatch, tmp_path, ahead):
+    from pico_vllm_b200 import SamplingParams
+    cfg = helpers.tiny_config("a")
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 7 + n) for n in (5, 17, 33)]
+    tensors = helpers.tiny_tensors("a", torch.float32)
+    want = [plain.greedy_generate(p, tensors, helpers.plain_config(cfg), 10) for p in prompts]
+    eos = want[1][3]                      # request 1 meets it as its 4th token
+    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=512, async_scheduling=ahead)
+    llm.scheduler.eos_token_id = eos
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=10))
+    for w, o in zip(want, outs):
+        cut = w.index(eos) + 1 if eos in w else len(w)
+        assert o.token_ids == w[:cut]
+        assert o.finish_reason == ("eos" if eos in w else "length")
+    llm.cache.check()
+    assert all(g.pool.in_use == 0 for g in llm.cache.groups) and llm.cache.free_slots == llm.cache.max_num_seqs
+    # the engine can go on after that
+    again = llm.generate(prompts[:1], SamplingParams(temperature=0.0, max_new_tokens=10, ignore_eos=True))
+    assert again[0].token_ids == want[0]
