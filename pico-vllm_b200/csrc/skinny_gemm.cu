@@ -51,6 +51,12 @@ struct SkinnyArgs {
     const bf16* w;            // [N, K]
     const bf16* x;            // [M, K] (row stride ldx)
     int ldx;
+    // or, instead of x: the float32 residual stream, to be RMS-normed on the way in (needs the
+    // activations-in-shared-memory mode): x[m, :] = xf[rows ? rows[m] : m, :] * rsqrt(mean(xf^2) + eps) * norm_w
+    const float* xf;          // [*, K]
+    const float* norm_w;      // [K]
+    const int* x_rows;        // [M] or null
+    float eps;
     int M, N, K;
     // STORE
     void* out;                // [M, ld_out] bf16 or float32
@@ -250,12 +256,46 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
             sg_commit();
         }
         pdl_wait();
-        const int chunks = (nk64 * SG_KW) >> 3;                  // per row, K rounded up to 64
-        for (int idx = threadIdx.x; idx < XR * chunks; idx += SG_THREADS) {
-            const int r = idx / chunks, c = idx - r * chunks;
-            const int k = c * 8;
-            const bool ok = k < p.K && r < p.M;
-            sg_cp16(sg_smem_u32(x_all + r * x_ld + k), p.x + (size_t)(ok ? r : 0) * p.ldx + (ok ? k : 0), ok);
+        if (p.xf) {
+            // RMS norm of the residual stream on the way in, float32, one warp per token row
+            // (y = x * rsqrt(mean(x^2) + eps) * w, pico_vllm/RMSNorm.py:22-34)
+            const int kpad = nk64 * SG_KW;
+            for (int r = warp; r < XR; r += SG_WARPS) {
+                bf16* dst = x_all + r * x_ld;
+                if (r >= p.M) {
+                    for (int k = lane * 2; k < kpad; k += 64) *reinterpret_cast<uint32_t*>(dst + k) = 0u;
+                    continue;
+                }
+                const float* src = p.xf + (size_t)(p.x_rows ? p.x_rows[r] : r) * p.K;
+                float ss = 0.f;
+                for (int k = lane * 4; k < p.K; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(src + k);
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+                ss = warp_sum(ss);
+                const float inv = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+                for (int k = lane * 4; k < kpad; k += 128) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f), w = v;
+                    if (k < p.K) {
+                        v = *reinterpret_cast<const float4*>(src + k);
+                        w = *reinterpret_cast<const float4*>(p.norm_w + k);
+                    }
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv * w.x, v.y * inv * w.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * inv * w.z, v.w * inv * w.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst + k) = pk;
+                }
+            }
+        } else {
+            const int chunks = (nk64 * SG_KW) >> 3;              // per row, K rounded up to 64
+            for (int idx = threadIdx.x; idx < XR * chunks; idx += SG_THREADS) {
+                const int r = idx / chunks, c = idx - r * chunks;
+                const int k = c * 8;
+                const bool ok = k < p.K && r < p.M;
+                sg_cp16(sg_smem_u32(x_all + r * x_ld + k), p.x + (size_t)(ok ? r : 0) * p.ldx + (ok ? k : 0), ok);
+            }
         }
         sg_commit();
         sg_wait<0>();            // once per block: the activations (and the first weight stages) have landed
@@ -316,6 +356,9 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
     sg_wait<0>();
 }
 
+// Do the activations of all of K fit in shared memory beside the weight rings (two blocks per SM)?
+static bool sg_xpre(int mt, int K) { return (size_t)mt * 8 * (K + 72) * sizeof(bf16) <= (mt == 1 ? 34 : 52) * 1024; }
+
 static int sg_num_sms() {
     static int sms = 0;
     if (!sms) {
@@ -342,7 +385,8 @@ static int sg_launch(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
     // persistent blocks, SG_CTAS_PER_SM per SM
     const int grid = tiles < SG_CTAS_PER_SM * sms ? tiles : SG_CTAS_PER_SM * sms;
     // the activations of all of K stay in shared memory when they fit beside the weight rings
-    const bool xpre = (size_t)mt * 8 * (a.K + 72) * sizeof(bf16) <= 34 * 1024;
+    const bool xpre = sg_xpre(mt, a.K);
+    if (a.xf && !xpre) return PICO_ERR_SIZE;
     // fewer tiles than SMs and a long K: one block per SM has to keep enough bytes in flight alone
     const bool deep = !xpre && tiles <= sms;
     if (mt == 1) {
@@ -350,7 +394,7 @@ static int sg_launch(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
         else if (deep) sg_launch_one<1, EPI, SG_ST_DEEP, false>(a, tiles, grid, stream);
         else sg_launch_one<1, EPI, SG_ST_STREAM, false>(a, tiles, grid, stream);
     } else if (mt == 2) {
-        if (xpre) sg_launch_one<2, EPI, SG_ST_XPRE, true>(a, tiles, grid, stream);
+        if (xpre) sg_launch_one<2, EPI, SG_ST_XPRE - 1, true>(a, tiles, grid, stream);
         else if (deep) sg_launch_one<2, EPI, SG_ST_DEEP * 3 / 4, false>(a, tiles, grid, stream);
         else sg_launch_one<2, EPI, SG_ST_STREAM * 3 / 4, false>(a, tiles, grid, stream);
     } else
@@ -363,12 +407,33 @@ static int sg_check(int M, int N, int K, int ldx) {
     return 0;
 }
 
+// Says whether the norm-on-the-way-in form takes these sizes (M tokens, inner size K).
+PICO_API int pico_skinny_norm_fits(int M, int K) {
+    return M >= 1 && M <= 16 && K % 16 == 0 && sg_xpre((M + 7) / 8, K) ? 1 : 0;
+}
+
+static void sg_set_x(SkinnyArgs& a, const void* x, int ldx, const float* norm_w, float eps, const int* x_rows) {
+    if (norm_w) {            // x is the float32 residual stream
+        a.xf = (const float*)x;
+        a.norm_w = norm_w;
+        a.eps = eps;
+        a.x_rows = x_rows;
+        a.x = nullptr;
+        a.ldx = 8;
+    } else {
+        a.x = (const bf16*)x;
+        a.ldx = ldx;
+    }
+}
+
 // y = x w^T (+ bias): out [M, ld_out] bfloat16 (out_f32 = 0) or float32 (1).  N % 16 == 0.
+// With norm_w: x is the float32 residual stream [*, K] (rows x_rows[m] or m) and is RMS-normed on the way in.
 PICO_API int pico_skinny_linear(const void* x, int ldx, const void* w, const float* bias, void* out, int ld_out,
-                                int out_f32, int M, int N, int K, cudaStream_t stream) {
-    if (sg_check(M, N, K, ldx) || N % 16 != 0) return PICO_ERR_SIZE;
+                                int out_f32, int M, int N, int K, const float* norm_w, float eps, const int* x_rows,
+                                cudaStream_t stream) {
+    if (sg_check(M, N, K, norm_w ? 8 : ldx) || N % 16 != 0) return PICO_ERR_SIZE;
     SkinnyArgs a = {};
-    a.w = (const bf16*)w; a.x = (const bf16*)x; a.ldx = ldx; a.M = M; a.N = N; a.K = K;
+    a.w = (const bf16*)w; sg_set_x(a, x, ldx, norm_w, eps, x_rows); a.M = M; a.N = N; a.K = K;
     a.out = out; a.ld_out = ld_out; a.out_f32 = out_f32; a.bias = bias;
     return sg_launch<SG_STORE>(a, N / 16, stream);
 }
@@ -384,10 +449,10 @@ PICO_API int pico_skinny_linear_residual(const void* x, int ldx, const void* w, 
 
 // out[M, I] = silu(x wg^T) * (x wu^T) with w = [wg; wu] of shape [2I, K].  I % 8 == 0.
 PICO_API int pico_skinny_gate_up_swiglu(const void* x, int ldx, const void* w, void* out, int M, int I, int K,
-                                        cudaStream_t stream) {
-    if (sg_check(M, 2 * I, K, ldx) || I % 8 != 0) return PICO_ERR_SIZE;
+                                        const float* norm_w, float eps, cudaStream_t stream) {
+    if (sg_check(M, 2 * I, K, norm_w ? 8 : ldx) || I % 8 != 0) return PICO_ERR_SIZE;
     SkinnyArgs a = {};
-    a.w = (const bf16*)w; a.x = (const bf16*)x; a.ldx = ldx; a.M = M; a.N = 2 * I; a.K = K;
+    a.w = (const bf16*)w; sg_set_x(a, x, ldx, norm_w, eps, nullptr); a.M = M; a.N = 2 * I; a.K = K;
     a.out = out; a.ld_out = I;
     return sg_launch<SG_SWIGLU>(a, I / 8, stream);
 }
@@ -398,11 +463,11 @@ PICO_API int pico_skinny_gate_up_swiglu(const void* x, int ldx, const void* w, v
 PICO_API int pico_skinny_qkv_rope_store(const void* x, int ldx, const void* w, const float* bias, void* q_out,
                                         const int* positions, const float* inv_freq, int rot_dim, const int* slots,
                                         void* k_pages, void* v_pages, int M, int K, int nh, int nkv, int hd,
-                                        int page_size, cudaStream_t stream) {
+                                        int page_size, const float* norm_w, float eps, cudaStream_t stream) {
     const int N = (nh + 2 * nkv) * hd;
-    if (sg_check(M, N, K, ldx) || hd % 16 != 0 || rot_dim % 2 != 0 || rot_dim > hd) return PICO_ERR_SIZE;
+    if (sg_check(M, N, K, norm_w ? 8 : ldx) || hd % 16 != 0 || rot_dim % 2 != 0 || rot_dim > hd) return PICO_ERR_SIZE;
     SkinnyArgs a = {};
-    a.w = (const bf16*)w; a.x = (const bf16*)x; a.ldx = ldx; a.M = M; a.N = N; a.K = K; a.bias = bias;
+    a.w = (const bf16*)w; sg_set_x(a, x, ldx, norm_w, eps, nullptr); a.M = M; a.N = N; a.K = K; a.bias = bias;
     a.nh = nh; a.nkv = nkv; a.hd = hd; a.rot_half = rot_dim / 2; a.page_size = page_size;
     a.positions = positions; a.slots = slots; a.inv_freq = inv_freq;
     a.q_out = (bf16*)q_out; a.k_pages = (bf16*)k_pages; a.v_pages = (bf16*)v_pages;

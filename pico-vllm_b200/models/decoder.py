@@ -95,5 +95,8 @@ class DecoderModel:
             x, pending = self.blocks[call.block].forward(x, pending, batch, view)
         if batch.num_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=x.device)
+        if pending is None and hasattr(self.head, "can_fuse_norm") \
+                and self.head.can_fuse_norm(x, self.final_norm, batch.num_logit_rows):
+            return self.head.forward_normed(x, self.final_norm, batch.logit_rows)
         y = self.final_norm.add_norm(x, pending, rows=batch.logit_rows)
         return self.head.forward(y)

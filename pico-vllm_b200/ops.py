@@ -55,10 +55,12 @@ def library():
         "pico_paged_prefill_mma": [vp, i32, vp, vp, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
         "pico_paged_decode_mma": [vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                                   f32, i32, vp],
-        "pico_skinny_linear": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+        "pico_skinny_linear": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp, vp],
+        "pico_skinny_norm_fits": [i32, i32],
         "pico_skinny_linear_residual": [vp, i32, vp, vp, i32, i32, i32, vp],
-        "pico_skinny_gate_up_swiglu": [vp, i32, vp, vp, i32, i32, i32, vp],
-        "pico_skinny_qkv_rope_store": [vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+        "pico_skinny_gate_up_swiglu": [vp, i32, vp, vp, i32, i32, i32, vp, f32, vp],
+        "pico_skinny_qkv_rope_store": [vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, f32,
+                                       vp],
         "pico_make_kv_tensor_map": [vp, vp, i64, i32, i32],
         "pico_paged_decode_tma": [vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                                   f32, i32, vp],
@@ -353,17 +355,46 @@ def skinny_takes(x: torch.Tensor, weight: torch.Tensor, n_multiple: int = 16) ->
             and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous())
 
 
+def skinny_norm_takes(x: torch.Tensor, weight: torch.Tensor, n_rows: Optional[int] = None) -> bool:
+    """True when the small-batch kernels can take the float32 residual stream ``x`` [*, K] itself and
+    RMS-norm it on the way in (``n_rows`` rows of it, default all), instead of normed activations."""
+    M = x.shape[0] if n_rows is None else n_rows
+    return (x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and weight.dtype == torch.bfloat16
+            and weight.is_contiguous() and weight.shape[0] % 16 == 0 and weight.shape[0] >= 16
+            and weight.shape[1] == x.shape[1] and 1 <= M <= SKINNY_MAX_TOKENS
+            and library().pico_skinny_norm_fits(M, x.shape[1]) == 1)
+
+
+def _norm_args(x, norm_weight, what):
+    if norm_weight is None:
+        return None
+    if x.dtype != torch.float32 or not x.is_contiguous() or norm_weight.dtype != torch.float32 \
+            or norm_weight.shape != (x.shape[1],):
+        raise KernelError(f"{what}: with a norm weight, x must be the contiguous float32 residual stream")
+    return norm_weight
+
+
 def skinny_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                  out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """x [M<=16, K] times weight[N, K] transposed (+ bias), bfloat16 in, out bfloat16 or float32."""
-    _cuda(x, weight, bias)
-    if not skinny_takes(x, weight):
-        raise KernelError("skinny_linear: needs bfloat16, at most 16 tokens, K and N multiples of 16")
-    M, K = x.shape
+                  out_dtype: torch.dtype = torch.bfloat16, norm_weight: Optional[torch.Tensor] = None,
+                  eps: float = 0.0, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [M<=16, K] times weight[N, K] transposed (+ bias), bfloat16 in, out bfloat16 or float32.
+    With ``norm_weight``: x is the float32 residual stream and is RMS-normed on the way in
+    (``rows`` int32 picks the rows to use)."""
+    _cuda(x, weight, bias, norm_weight, rows)
+    if _norm_args(x, norm_weight, "skinny_linear") is not None:
+        M = rows.shape[0] if rows is not None else x.shape[0]
+        if not skinny_norm_takes(x, weight, M) or (rows is not None and rows.dtype != torch.int32):
+            raise KernelError("skinny_linear: sizes not taken with a fused norm")
+    else:
+        if not skinny_takes(x, weight):
+            raise KernelError("skinny_linear: needs bfloat16, at most 16 tokens, K and N multiples of 16")
+        M = x.shape[0]
+    K = x.shape[1]
     N = weight.shape[0]
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _check(library().pico_skinny_linear(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(out), N,
-                                        1 if out_dtype == torch.float32 else 0, M, N, K, _stream()), "skinny_linear")
+                                        1 if out_dtype == torch.float32 else 0, M, N, K, _ptr(norm_weight),
+                                        float(eps), _ptr(rows), _stream()), "skinny_linear")
     _count()
     return out
 
@@ -381,16 +412,21 @@ def skinny_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torc
     _count()
 
 
-def skinny_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
-    """silu(x wg^T) * (x wu^T) for gate_up_weight = [wg; wu] ([2I, K]); returns [M, I] bfloat16."""
-    _cuda(x, gate_up_weight)
-    if not skinny_takes(x, gate_up_weight):
+def skinny_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
+                          eps: float = 0.0) -> torch.Tensor:
+    """silu(x wg^T) * (x wu^T) for gate_up_weight = [wg; wu] ([2I, K]); returns [M, I] bfloat16.
+    With ``norm_weight``: x is the float32 residual stream and is RMS-normed on the way in."""
+    _cuda(x, gate_up_weight, norm_weight)
+    if _norm_args(x, norm_weight, "skinny_gate_up_swiglu") is not None:
+        if not skinny_norm_takes(x, gate_up_weight):
+            raise KernelError("skinny_gate_up_swiglu: sizes not taken with a fused norm")
+    elif not skinny_takes(x, gate_up_weight):
         raise KernelError("skinny_gate_up_swiglu: needs bfloat16, at most 16 tokens, K and 2I multiples of 16")
     M, K = x.shape
     I = gate_up_weight.shape[0] // 2
     out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
     _check(library().pico_skinny_gate_up_swiglu(_ptr(x), x.stride(0), _ptr(gate_up_weight), _ptr(out), M, I, K,
-                                                _stream()), "skinny_gate_up_swiglu")
+                                                _ptr(norm_weight), float(eps), _stream()), "skinny_gate_up_swiglu")
     _count()
     return out
 
@@ -398,12 +434,16 @@ def skinny_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torc
 def skinny_qkv_rope_store(x: torch.Tensor, qkv_weight: torch.Tensor, bias: Optional[torch.Tensor],
                           positions: torch.Tensor, inv_freq: torch.Tensor, slots: Optional[torch.Tensor],
                           k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], n_heads: int,
-                          n_kv_heads: int, head_dim: int, page_size: int) -> torch.Tensor:
+                          n_kv_heads: int, head_dim: int, page_size: int,
+                          norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
     """qkv projection, bias, rotary encoding and cache store in one kernel; returns the rotated
-    queries [M, n_heads * head_dim] bfloat16.  Same meaning as ``linear`` + ``rope_store``."""
-    _cuda(x, qkv_weight, bias, positions, inv_freq, slots, k_pages, v_pages)
+    queries [M, n_heads * head_dim] bfloat16.  Same meaning as ``linear`` + ``rope_store``.
+    With ``norm_weight``: x is the float32 residual stream and is RMS-normed on the way in."""
+    _cuda(x, qkv_weight, bias, positions, inv_freq, slots, k_pages, v_pages, norm_weight)
     M, K = x.shape
-    if not skinny_takes(x, qkv_weight) or head_dim % 16 != 0 \
+    takes = skinny_norm_takes(x, qkv_weight) if _norm_args(x, norm_weight, "skinny_qkv_rope_store") is not None \
+        else skinny_takes(x, qkv_weight)
+    if not takes or head_dim % 16 != 0 \
             or qkv_weight.shape[0] != (n_heads + 2 * n_kv_heads) * head_dim:
         raise KernelError("skinny_qkv_rope_store: sizes not taken")
     if bias is not None and (bias.dtype != torch.float32 or bias.shape != (qkv_weight.shape[0],)):
@@ -420,7 +460,8 @@ def skinny_qkv_rope_store(x: torch.Tensor, qkv_weight: torch.Tensor, bias: Optio
     _check(library().pico_skinny_qkv_rope_store(_ptr(x), x.stride(0), _ptr(qkv_weight), _ptr(bias), _ptr(q),
                                                 _ptr(positions), _ptr(inv_freq), 2 * inv_freq.shape[0], _ptr(slots),
                                                 _ptr(k_pages), _ptr(v_pages), M, K, n_heads, n_kv_heads, head_dim,
-                                                page_size, _stream()), "skinny_qkv_rope_store")
+                                                page_size, _ptr(norm_weight), float(eps), _stream()),
+           "skinny_qkv_rope_store")
     _count()
     return q
 

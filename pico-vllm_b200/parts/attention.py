@@ -45,12 +45,26 @@ class GQAAttention(Part):
     def materialize(self, device, dtype):
         self.position.materialize(device, dtype)
 
-    def forward(self, h: torch.Tensor, batch, cache: CacheView, residual: Optional[torch.Tensor] = None):
+    def can_fuse_norm(self, x: torch.Tensor, norm) -> bool:
+        """True when forward can take the residual stream itself and apply ``norm`` inside its
+        first kernel (small batches)."""
+        return hasattr(norm, "eps") and getattr(norm, "weight", None) is not None \
+            and ops.skinny_norm_takes(x, self.qkv_weight)
+
+    def forward(self, h: Optional[torch.Tensor], batch, cache: CacheView, residual: Optional[torch.Tensor] = None,
+                norm=None):
         """Returns what is to be added to the residual stream - or, when ``residual`` is given
-        and the fused small-batch kernels take the sizes, adds it there itself and returns None."""
+        and the fused small-batch kernels take the sizes, adds it there itself and returns None.
+        With ``norm`` (after ``can_fuse_norm``), ``h`` is None and the normed input is computed from
+        ``residual`` inside the first kernel."""
         gb = batch.groups[cache.group]
         slots = gb.slots if cache.store else None
-        if ops.skinny_takes(h, self.qkv_weight):
+        if norm is not None:
+            qkv = ops.skinny_qkv_rope_store(residual, self.qkv_weight, self.qkv_bias, batch.positions,
+                                            self.position.inv_freq, slots, cache.k, cache.v, self.n_heads,
+                                            self.n_kv_heads, self.head_dim, cache.page_size, norm.weight, norm.eps)
+            h = qkv             # only its dtype and device are used below
+        elif ops.skinny_takes(h, self.qkv_weight):
             # a handful of tokens: projection, bias, rotation and cache store are one kernel
             qkv = ops.skinny_qkv_rope_store(h, self.qkv_weight, self.qkv_bias, batch.positions,
                                             self.position.inv_freq, slots, cache.k, cache.v, self.n_heads,

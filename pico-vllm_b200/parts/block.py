@@ -24,14 +24,18 @@ class PreNormBlock:
                 cache: CacheView) -> Tuple[torch.Tensor, torch.Tensor]:
         """x: float32 residual stream [T, width]; pending: output of the previous part that is
         still to be added to x (or None).  Returns (x, pending) in the same sense."""
-        h = self.norm1.add_norm(x, pending)
-        a = self._call(self.mixer, x, h, batch, cache)
-        h = self.norm2.add_norm(x, a)
-        return x, self._call(self.feed_forward, x, h, batch)
+        a = self._run(self.norm1, self.mixer, x, pending, batch, cache)
+        return x, self._run(self.norm2, self.feed_forward, x, a, batch)
 
     @staticmethod
-    def _call(part, x, *args):
-        # a part that says ``fuses_residual`` may add its output to x itself and return None
-        if getattr(part, "fuses_residual", False):
-            return part.forward(*args, residual=x)
-        return part.forward(*args)
+    def _run(norm, part, x, pending, *args):
+        """norm, then the part.  A part that says ``fuses_residual`` may add its output to x itself
+        and return None; one that also has ``can_fuse_norm`` may take x and the norm instead of
+        normed activations (when nothing is pending to be added first)."""
+        fuses = getattr(part, "fuses_residual", False)
+        if fuses and pending is None and hasattr(part, "can_fuse_norm") and part.can_fuse_norm(x, norm):
+            return part.forward(None, *args, residual=x, norm=norm)
+        h = norm.add_norm(x, pending)
+        if fuses:
+            return part.forward(h, *args, residual=x)
+        return part.forward(h, *args)

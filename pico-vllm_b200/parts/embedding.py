@@ -39,6 +39,16 @@ class OutputHead(Part):
             return []
         return [Param("weight", (Piece("weight", (self.vocab, self.width)),))]
 
+    def matrix(self) -> torch.Tensor:
+        return self.tied_to.weight if self.tied_to is not None else self.weight
+
     def forward(self, y: torch.Tensor) -> torch.Tensor:
-        w = self.tied_to.weight if self.tied_to is not None else self.weight
-        return ops.logits_linear(y, w)
+        return ops.logits_linear(y, self.matrix())
+
+    def can_fuse_norm(self, x: torch.Tensor, norm, n_rows: int) -> bool:
+        return hasattr(norm, "eps") and getattr(norm, "weight", None) is not None \
+            and ops.skinny_norm_takes(x, self.matrix(), n_rows)
+
+    def forward_normed(self, x: torch.Tensor, norm, rows: torch.Tensor) -> torch.Tensor:
+        """Logits of rows ``rows`` of the residual stream x, with the last norm applied inside the kernel."""
+        return ops.skinny_linear(x, self.matrix(), None, torch.float32, norm.weight, norm.eps, rows)

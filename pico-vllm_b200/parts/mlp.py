@@ -30,10 +30,18 @@ class GatedMLP(Part):
                                          Piece("up.weight", (self.inner, self.width)))),
                 Param("down_weight", (Piece("down.weight", (self.width, self.inner)),))]
 
-    def forward(self, h: torch.Tensor, batch, residual: Optional[torch.Tensor] = None):
+    def can_fuse_norm(self, x: torch.Tensor, norm) -> bool:
+        return hasattr(norm, "eps") and getattr(norm, "weight", None) is not None and self.inner % 8 == 0 \
+            and ops.skinny_norm_takes(x, self.gate_up_weight)
+
+    def forward(self, h: Optional[torch.Tensor], batch, residual: Optional[torch.Tensor] = None, norm=None):
         """Returns what is to be added to the residual stream - or, when ``residual`` is given
-        and the fused small-batch kernels take the sizes, adds it there itself and returns None."""
-        if ops.skinny_takes(h, self.gate_up_weight) and self.inner % 8 == 0:
+        and the fused small-batch kernels take the sizes, adds it there itself and returns None.
+        With ``norm`` (after ``can_fuse_norm``), ``h`` is None and the normed input is computed from
+        ``residual`` inside the first kernel."""
+        if norm is not None:
+            a = ops.skinny_gate_up_swiglu(residual, self.gate_up_weight, norm.weight, norm.eps)
+        elif ops.skinny_takes(h, self.gate_up_weight) and self.inner % 8 == 0:
             a = ops.skinny_gate_up_swiglu(h, self.gate_up_weight)      # product and activation in one kernel
         else:
             gu = ops.linear(h, self.gate_up_weight)

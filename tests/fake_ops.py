@@ -117,7 +117,22 @@ def skinny_takes(x, weight, n_multiple=16):
             and x.shape[1] % 16 == 0 and weight.shape[0] % n_multiple == 0 and weight.shape[0] >= 16)
 
 
-def skinny_linear(x, weight, bias=None, out_dtype=torch.bfloat16):
+def skinny_norm_takes(x, weight, n_rows=None):
+    M = x.shape[0] if n_rows is None else n_rows
+    return x.dtype == torch.float32 and weight.dtype == torch.bfloat16 and 1 <= M <= 16 and x.shape[1] % 16 == 0 \
+        and weight.shape[0] % 16 == 0 and x.shape[1] <= 2000
+
+
+def _normed(x, norm_weight, eps, rows=None):
+    if norm_weight is None:
+        return x
+    if rows is not None:
+        x = x[rows.long()]
+    return plain.rms_norm(x.float(), norm_weight, eps).to(torch.bfloat16)
+
+
+def skinny_linear(x, weight, bias=None, out_dtype=torch.bfloat16, norm_weight=None, eps=0.0, rows=None):
+    x = _normed(x, norm_weight, eps, rows)
     y = x.float() @ weight.float().t()
     if bias is not None:
         y = y + bias
@@ -128,7 +143,8 @@ def skinny_linear_residual(x, weight, residual):
     residual.add_(x.float() @ weight.float().t())
 
 
-def skinny_gate_up_swiglu(x, gate_up_weight):
+def skinny_gate_up_swiglu(x, gate_up_weight, norm_weight=None, eps=0.0):
+    x = _normed(x, norm_weight, eps)
     gu = x.float() @ gate_up_weight.float().t()
     I = gu.shape[1] // 2
     g, u = gu[:, :I], gu[:, I:]
@@ -136,7 +152,8 @@ def skinny_gate_up_swiglu(x, gate_up_weight):
 
 
 def skinny_qkv_rope_store(x, qkv_weight, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads,
-                          head_dim, page_size):
+                          head_dim, page_size, norm_weight=None, eps=0.0):
+    x = _normed(x, norm_weight, eps)
     qkv = x.float() @ qkv_weight.float().t()          # float32 until after the rotation, like the kernel
     rope_store(qkv, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads, head_dim, page_size)
     return qkv[:, :n_heads * head_dim].to(torch.bfloat16)
@@ -177,7 +194,7 @@ def sample(logits, temperature, top_p, uniform, out):
 
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
-         "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "skinny_takes", "skinny_linear", "skinny_linear_residual",
+         "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
          "linear", "logits_linear", "sample"]
 

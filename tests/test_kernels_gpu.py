@@ -306,6 +306,48 @@ def test_skinny_qkv_rope_store(M, nh, nkv, hd, ps, rot, K):
     assert torch.allclose(q2.cpu().float(), qr.float(), **t) and torch.equal(kg2.cpu(), k0)
 
 
+@pytest.mark.parametrize("M", [1, 8, 11, 16])
+@pytest.mark.parametrize("K,eps", [(64, 1e-6), (1536, 1e-6), (192, 1e-5), (80, 1e-3)])
+def test_skinny_kernels_with_the_norm_inside(M, K, eps):
+    """The residual stream goes in as float32 and is RMS-normed inside the product kernels."""
+    from pico_vllm_b200 import ops
+    T = M + 3
+    x = torch.randn(T, K, generator=gen(80)) * 2
+    nw = 1 + 0.1 * torch.randn(K, generator=gen(81))
+    rows = torch.randperm(T, generator=gen(82))[:M].to(torch.int32)
+    # head: chosen rows, float32 logits
+    N = 272
+    w = (torch.randn(N, K, generator=gen(83)) / math.sqrt(K)).to(torch.bfloat16)
+    if not ops.skinny_norm_takes(x.to(DEV), w.to(DEV), M):
+        assert M > 8 and K > 1000
+        return
+    got = ops.skinny_linear(x.to(DEV), w.to(DEV), None, torch.float32, nw.to(DEV), eps, rows.to(DEV)).cpu()
+    want = fake_ops.skinny_linear(x, w, None, torch.float32, nw, eps, rows)
+    assert torch.allclose(got, want, atol=3e-2, rtol=2e-2)
+    # gate_up + swiglu on the first M rows
+    I = 176
+    wgu = (torch.randn(2 * I, K, generator=gen(84)) * 2 / math.sqrt(K)).to(torch.bfloat16)
+    got = ops.skinny_gate_up_swiglu(x[:M].contiguous().to(DEV), wgu.to(DEV), nw.to(DEV), eps).cpu().float()
+    want = fake_ops.skinny_gate_up_swiglu(x[:M], wgu, nw, eps).float()
+    assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
+    # qkv + rope + store
+    nh, nkv, hd, ps, pages = 4, 2, 16, 8, 6
+    wq = (torch.randn((nh + 2 * nkv) * hd, K, generator=gen(85)) / math.sqrt(K)).to(torch.bfloat16)
+    bias = 0.3 * torch.randn((nh + 2 * nkv) * hd, generator=gen(86))
+    pos = torch.randint(0, 900, (M,), generator=gen(87), dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd))
+    slots = torch.randperm(pages * ps, generator=gen(88))[:M].to(torch.int32)
+    k0 = torch.zeros(pages, nkv, ps, hd, dtype=torch.bfloat16)
+    kg, vg = k0.to(DEV), k0.to(DEV)
+    qg = ops.skinny_qkv_rope_store(x[:M].contiguous().to(DEV), wq.to(DEV), bias.to(DEV), pos.to(DEV), inv.to(DEV),
+                                   slots.to(DEV), kg, vg, nh, nkv, hd, ps, nw.to(DEV), eps)
+    kr, vr = k0.clone(), k0.clone()
+    qr = fake_ops.skinny_qkv_rope_store(x[:M], wq, bias, pos, inv, slots, kr, vr, nh, nkv, hd, ps, nw, eps)
+    t = dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(qg.cpu().float(), qr.float(), **t)
+    assert torch.allclose(kg.cpu().float(), kr.float(), **t) and torch.allclose(vg.cpu().float(), vr.float(), **t)
+
+
 def test_refuses_head_sizes_it_does_not_take():
     from pico_vllm_b200 import ops
     from pico_vllm_b200.errors import KernelError
