@@ -35,6 +35,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 
+// 2^x on the special-function unit (ex2.approx: about 2 ulp in float32; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Running softmax over one tile of scores for the two rows a thread holds (lane/4 and lane/4+8).
 // s: scores already scaled to log2 units and masked with -inf.  On return s holds p = 2^(s - m).
 template <int HD_MAX, int NT>
@@ -49,11 +56,11 @@ __device__ __forceinline__ void online_softmax(float (&s)[NT][4], float (&m)[2],
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(m[r], mx);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;      // a row that has seen no key yet
-        const float corr = exp2f(m[r] - m_use);                      // m = -inf gives 0
+        const float corr = fast_exp2(m[r] - m_use);                      // m = -inf gives 0
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-            const float p0 = exp2f(s[j][2 * r] - m_use), p1 = exp2f(s[j][2 * r + 1] - m_use);
+            const float p0 = fast_exp2(s[j][2 * r] - m_use), p1 = fast_exp2(s[j][2 * r + 1] - m_use);
             s[j][2 * r] = p0;
             s[j][2 * r + 1] = p1;
             sum += p0 + p1;

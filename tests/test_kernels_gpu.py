@@ -228,6 +228,23 @@ def test_tma_decode_split_keys(splits, window, nh, nkv, hd, ps):
     assert torch.allclose(got, want, **MMA_TOL)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(6, 2, 64, 16), (12, 2, 128, 16), (7, 1, 128, 8), (16, 1, 64, 32), (4, 4, 128, 64),
+                                          (28, 4, 128, 16)])
+@pytest.mark.parametrize("window", [None, 24, 200])
+def test_tma_attention_mixed_segments(nh, nkv, hd, ps, window):
+    got, want = _attention_case(torch.bfloat16, nh, nkv, hd, ps, window, seg_lens=[300, 133, 9, 1, 70, 2, 64, 190],
+                                q_lens=[257, 1, 2, 1, 33, 2, 1, 64], splits=1, mma=True, tma=True, poison=True)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("window,q_lens", [(None, [200, 150]), (64, [200, 150]), (None, [2, 300]), (100, [517, 64])])
+def test_tma_prefill_far_key_and_window_edge(window, q_lens):
+    got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=q_lens, splits=1,
+                                seed=5, spike=True, mma=True, tma=True, poison=True)
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
 @pytest.mark.parametrize("window,splits", [(None, 1), (None, 8), (64, 1), (64, 4)])
 def test_tma_decode_far_key_and_window_edge(window, splits):
     got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=[1, 1], splits=splits,
