@@ -252,6 +252,86 @@ def prefill_phase(llm, T, reps, seed):
     return times[len(times) // 2]
 
 
+def run_micro(args):
+    """Single kernels replayed from a CUDA graph over operands larger than L2 (rotating copies of
+    the weights, or the caches of many layers), timed with CUDA events: the figures that the
+    summaries under profiles/ quote beside the profiler's.  Prints one JSON line."""
+    import math
+    import torch
+    import pico_vllm_b200  # noqa: F401
+    from pico_vllm_b200 import ops
+    dev = "cuda:0"
+    M = args.batch
+
+    def graph_time(fns):
+        for f in fns[:3]:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            best = min(best, a.elapsed_time(b) * 1000 / len(fns))
+        return best
+
+    out = {"micro": True, "tokens": M, "context": args.context}
+    shapes = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960),
+              "head": (151936, 1536)}
+    for name, (N, K) in shapes.items():
+        mb = N * K * 2 / 1e6
+        copies = max(2, int(600 / mb) + 1)
+        ws = [(torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16() for _ in range(copies)]
+        x = torch.randn(M, K, device=dev).bfloat16()
+        res = torch.zeros(M, N, device=dev)
+        if name == "gate_up":
+            mk = lambda w: (lambda: ops.skinny_gate_up_swiglu(x, w))
+        elif name in ("o", "down"):
+            mk = lambda w: (lambda: ops.skinny_linear_residual(x, w, res))
+        elif name == "head":
+            mk = lambda w: (lambda: ops.skinny_linear(x, w, None, torch.float32))
+        else:
+            mk = lambda w: (lambda: ops.skinny_linear(x, w))
+        t = graph_time([mk(w) for w in ws] * 2)
+        tc = graph_time([(lambda w=w: torch.mm(x, w.t())) for w in ws] * 2)
+        out[f"skinny_{name}"] = {"us": round(t, 1), "GBps": round(mb / t * 1e3), "cublas_us": round(tc, 1)}
+        del ws
+    nh, nkv, hd, ps, L, ctx = 12, 2, 128, 16, 24, args.context
+    blocks = ctx // ps
+    pages = M * blocks
+    k = torch.randn(L, pages, nkv, ps, hd, device=dev).bfloat16()
+    v = torch.randn(L, pages, nkv, ps, hd, device=dev).bfloat16()
+    table = torch.randperm(pages, device=dev).int().view(M, blocks).contiguous()
+    q = torch.randn(M, nh * hd, device=dev).bfloat16()
+    seg = torch.arange(M, device=dev).int()
+    pos = torch.full((M,), ctx - 1, device=dev).int()
+    cu = torch.arange(M + 1, device=dev).int()
+    o = torch.empty(M, nh * hd, device=dev).bfloat16()
+    maps = [(ops.make_kv_tensor_map(k[l]), ops.make_kv_tensor_map(v[l])) for l in range(L)]
+    mb = M * ctx * nkv * hd * 2 * 2 / 1e6
+    want = 16 if M * nkv * 16 <= 148 else min(296 // (M * nkv), 8)
+    want = max(1, min(want, ctx // 128))
+    best_splits = 1
+    while best_splits * 2 <= want:
+        best_splits *= 2
+    for splits in sorted({best_splits, max(1, best_splits // 2)}):
+        scratch = torch.empty(max(1, ops.attention_scratch_floats(M, nh, hd, splits)), device=dev)
+        t = graph_time([(lambda l=l: ops.paged_attention_mma(q, k[l], v[l], o, seg, pos, table, cu, None, 0, 0, None, M,
+                                                             nh, nkv, hd, ps, None, 1 / math.sqrt(hd), splits, scratch,
+                                                             *maps[l])) for l in range(L)])
+        out[f"decode_attention_splits{splits}"] = {"us": round(t, 1), "GBps": round(mb / t * 1e3), "MB": round(mb, 1)}
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
     import torch
     if not torch.cuda.is_available():
@@ -347,6 +427,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase only and print a short line (for profiling; not a bench value)")
+    ap.add_argument("--micro", action="store_true",
+                    help="time single decode kernels replayed from a graph (skinny products, decode attention)")
     ap.add_argument("--profile-range", choices=["decode", "prefill"], default=None,
                     help="bracket that phase's timed region with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -364,6 +446,8 @@ def main():
     PROFILE_RANGE = args.profile_range
     if args.only:
         args.no_points = True
+    if args.micro:
+        return run_micro(args)
     return run_ours(args)
 
 

@@ -19,9 +19,9 @@
 #include <cuda.h>
 #include "mma_helpers.cuh"
 
-#ifndef TMA_STAGES
-#define TMA_STAGES 3
-#endif
+#define TMA_STAGES_FEW 4
+// stages when there is at most one block per SM (it must keep the SM's loads in flight alone)
+#define TMA_STAGES_MANY 3      // stages with two blocks per SM
 #define TMA_WAIT_LIMIT (1 << 22)
 #ifndef TMA_L2_PROMO
 #define TMA_L2_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
@@ -71,7 +71,23 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
         : "memory");
 }
+// thread-block cluster: barrier over all threads of all blocks, and loads from another block's shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
+    uint32_t raddr;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(raddr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+template <int NTHREADS> __device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;\n" ::"n"(NTHREADS) : "memory");
+}
 
 // A tile is [64 cache positions][HD] bfloat16, rows of HD*2 bytes, made of 128-byte segments that
 // TMA stores in its 128-byte swizzle: the 16-byte piece c of segment number s (counted from the
@@ -86,14 +102,17 @@ __device__ __forceinline__ uint32_t swz_addr(uint32_t tile, int key, int dim) {
 // copies of stage s have landed (transaction count); empty[s]: the four consumer warps are done
 // with stage s.
 #define TMA_THREADS 160
-template <int HD>     // head size: 64 or 128 (a multiple of 64)
-__global__ void __launch_bounds__(TMA_THREADS)
+// CW consumer warps in groups of four: group i takes tiles i, i + CW/4, ... (a group multiplies one tile,
+// 16 cache positions per warp).  One group is latency-bound at about 0.8 us per tile, so with one
+// block per SM two groups are used; with two blocks per SM one group each.
+template <int HD, int TMA_STAGES, int CW>     // head size 64 or 128; stages; consumer warps (4 or 8)
+__global__ void __launch_bounds__((CW + 1) * 32)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
                         float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ tok_list,
                         const int* __restrict__ tok_seg, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_stride, int nh, int nkv, int page_size,
-                        int window, float scale_log2, int n_splits) {
+                        int window, float scale_log2, int n_splits, int cluster_reduce) {
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_dyn[];
     constexpr int TILE_BYTES = MMA_BN * HD * 2;                  // one K or V tile
@@ -120,7 +139,11 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
-    pdl_wait();             // everything below reads what earlier kernels and copies wrote
+    // Token lists, positions and block tables come from the host copy at the start of the step and
+    // the cache of earlier positions from earlier steps: all of that may be read now.  What the
+    // kernel before this one wrote - the queries, and the key/value of the token's own position -
+    // is read only after pdl_wait(): by the consumers before they load the queries, by the producer
+    // before it copies the tile that holds the token's own position.
     const int t = tok_list ? tok_list[blockIdx.z] : blockIdx.z;
     const int pos = positions[t];
     const int hi = pos + 1;                                      // pos = -1 (padding): no keys at all
@@ -136,43 +159,57 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     {   // the block-table entries of this block's range, read once and together
         const int first_entry = t_begin * ppt;
         const int n_entries = min(ntiles * ppt, TMA_TABLE_CACHE);
-        for (int i = threadIdx.x; i < n_entries; i += TMA_THREADS)
+        for (int i = threadIdx.x; i < n_entries; i += (CW + 1) * 32)
             tbl_s[i] = first_entry + i < table_stride ? table[first_entry + i] : 0;
     }
     __syncthreads();                                             // barriers are initialised, the table is there
 
-    if (warp == 4) {
+    if (warp == CW) {
         // ---------------------------------------------------------------- producer
-        if (lane == 0) {
-            for (int it = 0; it < ntiles; ++it) {
-                const int s = it % TMA_STAGES;
-                if (it >= TMA_STAGES && !mbar_wait(empty + s, ((it / TMA_STAGES) - 1) & 1)) {
-                    g_tma_status = 1;
-                    *abort_s = 1;
-                }
-                if (*abort_s) break;
-                const int n0 = (t_begin + it) * MMA_BN;
-                unsigned char* kt = tiles + (size_t)s * 2 * TILE_BYTES;
-                unsigned char* vt = kt + TILE_BYTES;
-                // pages wholly outside [lo, hi) are skipped: they may have been given back (a window) or
-                // not exist yet
-                int first = 0, last = ppt;
-                while (first < last && n0 + (first + 1) * page_size <= lo) ++first;
-                while (last > first && n0 + (last - 1) * page_size >= hi) --last;
-                mbar_expect_tx(full + s, (uint32_t)((last - first) * page_size * HD * 2 * 2));
-                for (int pg = first; pg < last; ++pg) {
-                    const int e = it * ppt + pg;
-                    const int page = e < TMA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
-                    const int row = (page * nkv + kh) * page_size;
-                    tma_load_3d(kt + pg * page_size * HD * 2, &k_map, 0, 0, row, full + s);
-                    tma_load_3d(vt + pg * page_size * HD * 2, &v_map, 0, 0, row, full + s);
-                }
+        // One copy costs its issuing thread a few hundred cycles, so the copies of a tile are issued
+        // by different lanes: lane 2*pg copies page pg of the keys, lane 2*pg+1 of the values.
+        bool waited = false;
+        for (int it = 0; it < ntiles; ++it) {
+            const int s = it % TMA_STAGES;
+            if (it >= TMA_STAGES && !mbar_wait(empty + s, ((it / TMA_STAGES) - 1) & 1)) {
+                g_tma_status = 1;
+                *abort_s = 1;
             }
+            __syncwarp();
+            if (*abort_s) break;
+            const int n0 = (t_begin + it) * MMA_BN;
+            if (!waited && n0 + MMA_BN > pos) {      // this tile holds the token's own key and value
+                pdl_wait();
+                waited = true;
+            }
+            unsigned char* kt = tiles + (size_t)s * 2 * TILE_BYTES;
+            // pages wholly outside [lo, hi) are skipped: they may have been given back (a window) or
+            // not exist yet
+            int first = 0, last = ppt;
+            while (first < last && n0 + (first + 1) * page_size <= lo) ++first;
+            while (last > first && n0 + (last - 1) * page_size >= hi) --last;
+            if (lane == 0) mbar_expect_tx(full + s, (uint32_t)((last - first) * page_size * HD * 2 * 2));
+            __syncwarp();
+            const int pg = lane >> 1;
+            if (pg >= first && pg < last) {
+                const int e = it * ppt + pg;
+                const int page = e < TMA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
+                const int row = (page * nkv + kh) * page_size;
+                tma_load_3d(kt + (lane & 1) * TILE_BYTES + pg * page_size * HD * 2, (lane & 1) ? &v_map : &k_map, 0, 0, row,
+                            full + s);
+            }
+        }
+        if (cluster_reduce) {        // every thread of the cluster takes part in its two barriers
+            cluster_sync_all();
+            cluster_sync_all();
         }
         return;
     }
-    // -------------------------------------------------------------------- consumers (warps 0..3)
-    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
+    // -------------------------------------------------------------------- consumers (warps 0..CW-1)
+    constexpr int NG = CW / 4;                                   // consumer groups
+    const int grp = warp >> 2, wq = warp & 3;
+    pdl_wait();                                                  // the queries come from the kernel before
+    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += CW * 32) {
         const int r = idx / (HD / 8), c = idx - r * (HD / 8);
         const bool ok = r < g;
         const bf16* src = q + (size_t)t * q_row_stride + (size_t)(kh * g + (ok ? r : 0)) * HD + c * 8;
@@ -180,7 +217,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     }
     cp_async_commit();
     cp_async_wait<0>();
-    consumer_sync();                                             // the queries are in shared memory
+    consumer_sync<CW * 32>();                                             // the queries are in shared memory
 
     float o[HD / 8][4];
 #pragma unroll
@@ -189,8 +226,12 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
     const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
     const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
+    // the queries are the same for every tile: their fragments stay in registers
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int k0 = 0; k0 < HD; k0 += 16) ldmatrix_x4(qf[k0 / 16], smem_u32(q_s + a_row * QLD + k0 + a_col));
 
-    for (int it = 0; it < ntiles; ++it) {
+    for (int it = grp; it < ntiles; it += NG) {
         const int s = it % TMA_STAGES;
         const int n0 = (t_begin + it) * MMA_BN;
         if (!mbar_wait(full + s, (it / TMA_STAGES) & 1)) {
@@ -200,19 +241,26 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         if (*abort_s) break;
         const uint32_t kt = smem_u32(tiles + (size_t)s * 2 * TILE_BYTES);
         const uint32_t vt = kt + TILE_BYTES;
-        const int kw = warp * 16;                                // this warp's 16 positions of the tile
+        const int kw = wq * 16;                                  // this warp's 16 positions of the tile
         const int w0 = n0 + kw;
         if (w0 < hi && w0 + 16 > lo) {
-            float sc[2][4];
+            // q.k over the head dimension in two independent chains (even and odd steps of 16), so
+            // that one tensor-core instruction does not wait for the one before it
+            float sc[2][4], sc2[2][4];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+            for (int j = 0; j < 2; ++j) {
+                sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+                sc2[j][0] = sc2[j][1] = sc2[j][2] = sc2[j][3] = 0.f;
+            }
 #pragma unroll
-            for (int k0 = 0; k0 < HD; k0 += 16) {
-                uint32_t a[4], b[4];
-                ldmatrix_x4(a, smem_u32(q_s + a_row * QLD + k0 + a_col));
+            for (int k0 = 0; k0 < HD; k0 += 32) {
+                uint32_t b[4], b2[4];
                 ldmatrix_x4(b, swz_addr<HD>(kt, kw + b_row, k0 + b_col));
-                mma_bf16(sc[0], a, b[0], b[1]);
-                mma_bf16(sc[1], a, b[2], b[3]);
+                ldmatrix_x4(b2, swz_addr<HD>(kt, kw + b_row, k0 + 16 + b_col));
+                mma_bf16(sc[0], qf[k0 / 16], b[0], b[1]);
+                mma_bf16(sc[1], qf[k0 / 16], b[2], b[3]);
+                mma_bf16(sc2[0], qf[k0 / 16 + 1], b2[0], b2[1]);
+                mma_bf16(sc2[1], qf[k0 / 16 + 1], b2[2], b2[3]);
             }
             bool edge = false;                                   // some of the 16 positions are not visible
 #pragma unroll
@@ -222,7 +270,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
                     const int n = w0 + j * 8 + (lane & 3) * 2 + (e & 1);
                     const bool vis = n >= lo && n < hi;
                     edge |= !vis;
-                    sc[j][e] = vis ? sc[j][e] * scale_log2 : -INFINITY;
+                    sc[j][e] = vis ? (sc[j][e] + sc2[j][e]) * scale_log2 : -INFINITY;
                 }
             online_softmax<HD, 2>(sc, m, l, o);
             // p.v: invisible positions have p = 0 exactly, but their value rows may hold anything
@@ -255,11 +303,14 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);                   // this warp is done with the stage
     }
-    consumer_sync();
-    if (*abort_s) return;
+    consumer_sync<CW * 32>();
+    const bool dead = *abort_s != 0;
+    if (dead && !cluster_reduce) return;
     // merge the four warps: (m, l, o) of each warp -> shared memory (all copies have landed and been used)
-    float* mo = reinterpret_cast<float*>(tiles);                // [4 warps][16 rows][HD]
-    float* mml = mo + 4 * 16 * HD;                              // [4][16][2]
+    float* mo = reinterpret_cast<float*>(tiles);                // [CW warps][16 rows][HD]
+    float* mml = mo + CW * 16 * HD;                             // [CW][16][2]
+    float* fin_o = mml + CW * 16 * 2;                           // [16][HD]: this block's result, not normalised
+    float* fin_ml = fin_o + 16 * HD;                            // [16][2]: its max (log2 units) and sum
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + r * 8;
@@ -274,19 +325,19 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
             mo[(warp * 16 + row) * HD + d + 1] = o[i][2 * r + 1];
         }
     }
-    consumer_sync();
+    consumer_sync<CW * 32>();
     const float LN2 = 0.6931471805599453f;
-    for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
+    for (int idx = threadIdx.x; idx < g * HD; idx += CW * 32) {
         const int row = idx / HD, d = idx - row * HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+        for (int w = 0; w < CW; ++w) M = fmaxf(M, mml[(w * 16 + row) * 2]);
         float L = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < CW; ++w) {
             const float mw = mml[(w * 16 + row) * 2];
             if (mw != -INFINITY) {
-                const float f = exp2f(mw - M);
+                const float f = fast_exp2(mw - M);
                 L += mml[(w * 16 + row) * 2 + 1] * f;
                 acc += mo[(w * 16 + row) * HD + d] * f;
             }
@@ -294,6 +345,12 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         const int h = kh * g + row;
         if (n_splits == 1) {
             out[((size_t)t * nh + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else if (cluster_reduce) {
+            fin_o[row * HD + d] = acc;
+            if (d == 0) {
+                fin_ml[row * 2] = M;
+                fin_ml[row * 2 + 1] = L;
+            }
         } else {
             const size_t slot = ((size_t)t * nh + h) * n_splits + sp;
             part_o[slot * HD + d] = acc;
@@ -303,6 +360,32 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
             }
         }
     }
+    if (!cluster_reduce || n_splits == 1) return;
+    // The splits of one (token, kv head) are the blocks of one cluster: each block adds, over all
+    // blocks, its share of the g * HD outputs, reading the others' results through distributed
+    // shared memory - no scratch in global memory, no second kernel.
+    cluster_sync_all();
+    {
+        const int total = g * HD;
+        const int share = (total + n_splits - 1) / n_splits;
+        const int lo_i = sp * share, hi_i = min(total, lo_i + share);
+        for (int idx = lo_i + (int)threadIdx.x; idx < hi_i; idx += CW * 32) {
+            const int row = idx / HD, d = idx - row * HD;
+            float M = -INFINITY;
+            for (int r = 0; r < n_splits; ++r) M = fmaxf(M, ld_cluster_f32(fin_ml + row * 2, r));
+            float L = 0.f, acc = 0.f;
+            for (int r = 0; r < n_splits; ++r) {
+                const float mr = ld_cluster_f32(fin_ml + row * 2, r);
+                if (mr != -INFINITY) {
+                    const float f = fast_exp2(mr - M);
+                    L += ld_cluster_f32(fin_ml + row * 2 + 1, r) * f;
+                    acc += ld_cluster_f32(fin_o + row * HD + d, r) * f;
+                }
+            }
+            out[((size_t)t * nh + kh * g + row) * HD + d] = __float2bfloat16_rn((L > 0.f && !dead) ? acc / L : 0.f);
+        }
+    }
+    cluster_sync_all();              // nobody leaves while others still read its shared memory
 }
 
 // ------------------------------------------------------------------------------------------ prefill
@@ -401,7 +484,7 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid
     }
     cp_async_commit();
     cp_async_wait<0>();
-    consumer_sync();
+    consumer_sync<128>();
 
     float o[HD / 8][4];
 #pragma unroll
@@ -556,6 +639,57 @@ __global__ void decode_combine_kernel(const float*, const float*, bf16*, const i
 int pico_launch_decode_combine(const float* part_o, const float* part_ml, void* out, const int* tok_list, int n_tok,
                                int nh, int hd, int n_splits, cudaStream_t stream);
 
+// Can clusters of `size` blocks of the decode kernel run here?  (Asked once per configuration.)
+template <int HD, int ST, int CW>
+static bool tma_cluster_query(int size, size_t smem) {
+    if (size > 8 && cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+                        cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(size, 1, 1);
+    cfg.blockDim = dim3((CW + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, paged_decode_tma_kernel<HD, ST, CW>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return n > 0;
+}
+static bool tma_cluster_ok(int hd, int size, bool few, size_t smem) {
+    static int cache[2][2][5];      // [hd 64/128][few][log2 size]: 0 unknown, 1 yes, 2 no
+    int lg = 0;
+    while ((1 << lg) < size) ++lg;
+    int& c = cache[hd == 128 ? 1 : 0][few ? 1 : 0][lg];
+    if (c == 0) {
+        bool ok;
+        if (hd == 128) ok = few ? tma_cluster_query<128, TMA_STAGES_FEW, 8>(size, smem) : tma_cluster_query<128, TMA_STAGES_MANY, 4>(size, smem);
+        else ok = few ? tma_cluster_query<64, TMA_STAGES_FEW, 8>(size, smem) : tma_cluster_query<64, TMA_STAGES_MANY, 4>(size, smem);
+        c = ok ? 1 : 2;
+    }
+    return c == 1;
+}
+
+static int tma_num_sms() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
 // Single tokens with TMA-fed tiles.  k_map / v_map: tensor maps made by pico_make_kv_tensor_map (host
 // pointers; they are copied into the kernel's parameters).  Other arguments as pico_paged_decode_mma.
 PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const void* q, int q_row_stride, void* out,
@@ -568,26 +702,38 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
     const int g = nh / nkv;
     if (g > 16 || nkv > 65535 || n_tok > 65535 || n_splits < 1 || n_splits > 64) return PICO_ERR_SIZE;
     if (page_size < 8 || MMA_BN % page_size != 0) return PICO_ERR_SIZE;
-    if (n_splits > 1 && (!part_o || !part_ml)) return PICO_ERR_SIZE;
     if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
     const dim3 grid(n_splits, nkv, n_tok);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)TMA_STAGES * 2 * MMA_BN * hd * 2 + (size_t)16 * (hd + 8) * 2 + 2 * TMA_STAGES * 8 + 8 +
+    const bool few = false;      // one block per SM with more stages or more consumer warps was measured slower: it keeps
+                                 // the next kernel's blocks (which prefetch under programmatic launch) off the SM
+    const int stages = few ? TMA_STAGES_FEW : TMA_STAGES_MANY;
+    const size_t smem = (size_t)stages * 2 * MMA_BN * hd * 2 + (size_t)16 * (hd + 8) * 2 + 2 * stages * 8 + 8 +
                         TMA_TABLE_CACHE * 4 + 1024;
     CUtensorMap km, vm;
     memcpy(&km, k_map, sizeof(CUtensorMap));
     memcpy(&vm, v_map, sizeof(CUtensorMap));
-#define LAUNCH_TMA(HD)                                                                                              \
-    do {                                                                                                            \
-        cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-        pico_launch((paged_decode_tma_kernel<HD>), dim3(grid), dim3(TMA_THREADS), smem, stream,                                            \
-            km, vm, (const bf16*)q, q_row_stride, (bf16*)out, part_o, part_ml, tok_list, tok_seg, positions,        \
-            block_table, table_stride, nh, nkv, page_size, window, scale_log2, n_splits);                           \
+    // 2, 4, 8 or 16 splits: the splits of one (token, kv head) run as one thread-block cluster and are
+    // added through distributed shared memory; otherwise through scratch and the combine kernel
+    int cluster = 0;
+    if (n_splits == 2 || n_splits == 4 || n_splits == 8 || n_splits == 16) cluster = tma_cluster_ok(hd, n_splits, few, smem) ? 1 : 0;
+    if (n_splits > 1 && !cluster && (!part_o || !part_ml)) return PICO_ERR_SIZE;
+#define LAUNCH_TMA(HD, ST, CW)                                                                                          \
+    do {                                                                                                                \
+        cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        pico_launch_cluster((paged_decode_tma_kernel<HD, ST, CW>), grid, dim3((CW + 1) * 32), smem, stream,             \
+                            cluster ? n_splits : 1, km, vm, (const bf16*)q, q_row_stride, (bf16*)out, part_o,           \
+                            part_ml, tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, page_size,       \
+                            window, scale_log2, n_splits, cluster);                                                     \
     } while (0)
-    if (hd == 64) LAUNCH_TMA(64);
-    else LAUNCH_TMA(128);
+    if (hd == 64) {
+        if (few) LAUNCH_TMA(64, TMA_STAGES_FEW, 8); else LAUNCH_TMA(64, TMA_STAGES_MANY, 4);
+    } else {
+        if (few) LAUNCH_TMA(128, TMA_STAGES_FEW, 8); else LAUNCH_TMA(128, TMA_STAGES_MANY, 4);
+    }
 #undef LAUNCH_TMA
-    if (n_splits > 1) return pico_launch_decode_combine(part_o, part_ml, out, tok_list, n_tok, nh, hd, n_splits, stream);
+    if (n_splits > 1 && !cluster)
+        return pico_launch_decode_combine(part_o, part_ml, out, tok_list, n_tok, nh, hd, n_splits, stream);
     return pico_launch_status();
 }
 

@@ -108,13 +108,17 @@ class ModelRunner:
         return self._stage
 
     def _splits(self, T: int, max_kv: int) -> int:
-        """How many parts to cut each token's key range into: as many as make one wave of blocks
-        (two per SM on 148 SMs) when the batch is small and the context long, each part at least
-        two tiles of 64 keys."""
-        blocks = max(1, T * self._min_kv_heads)
-        want = 296 // blocks
-        most = max_kv // 128
-        return int(max(1, min(want, most, 64)))
+        """How many parts to cut each token's key range into: a power of two (the parts of one token
+        and kv head run as one thread-block cluster): up to 16 when that still is at most one block
+        per SM, else up to 8 while the blocks make no more than one wave (two per SM on 148 SMs);
+        each part at least two tiles of 64 keys."""
+        groups = max(1, T * self._min_kv_heads)
+        want = 16 if groups * 16 <= 148 else min(296 // groups, 8)
+        want = min(want, max_kv // 128)
+        splits = 1
+        while splits * 2 <= want:
+            splits *= 2
+        return splits
 
     def _scratch_for(self, T: int, splits: int) -> Optional[torch.Tensor]:
         if splits <= 1:

@@ -346,7 +346,8 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                                              n_kv_heads, head_dim, page_size, win, float(scale), n_splits,
                                              _stream()),
                    f"paged_decode_mma (head_dim {head_dim})")
-        _count(2 if n_splits > 1 else 1)
+        clustered = k_map is not None and v_map is not None and n_splits in (2, 4, 8, 16)
+        _count(2 if n_splits > 1 and not clustered else 1)
     return out
 
 
