@@ -287,6 +287,8 @@ def run_micro(args):
     shapes = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960),
               "head": (151936, 1536)}
     for name, (N, K) in shapes.items():
+        if M > 16:
+            break               # the small-batch kernels take at most 16 tokens
         mb = N * K * 2 / 1e6
         copies = max(2, int(600 / mb) + 1)
         ws = [(torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16() for _ in range(copies)]
@@ -304,6 +306,22 @@ def run_micro(args):
         tc = graph_time([(lambda w=w: torch.mm(x, w.t())) for w in ws] * 2)
         out[f"skinny_{name}"] = {"us": round(t, 1), "GBps": round(mb / t * 1e3), "cublas_us": round(tc, 1)}
         del ws
+    if M >= 128:                # many tokens: the tcgen05 products against the library's
+        for name, (N, K) in shapes.items():
+            if name == "head":
+                continue
+            x = torch.randn(M, K, device=dev).bfloat16()
+            w = (torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16()
+            fl = 2.0 * M * N * K
+            if name == "gate_up":
+                t = graph_time([lambda: ops.tc_gate_up_swiglu(x, w)] * 8)
+            else:
+                t = graph_time([lambda: ops.tc_linear(x, w)] * 8)
+            tc = graph_time([lambda: torch.mm(x, w.t())] * 8)
+            out[f"tcgen05_{name}"] = {"us": round(t, 1), "tflops": round(fl / t / 1e6), "cublas_us": round(tc, 1),
+                                      "fused": "swiglu" if name == "gate_up" else None}
+        print(json.dumps(out))
+        return 0
     nh, nkv, hd, ps, L, ctx = 12, 2, 128, 16, 24, args.context
     blocks = ctx // ps
     pages = M * blocks

@@ -66,6 +66,8 @@ def library():
                                   f32, i32, vp],
         "pico_paged_prefill_tma": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
         "pico_tma_status": [vp],
+        "pico_gemm_tcgen05": [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp],
+        "pico_tc_status": [vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_bf16_to_f32": [vp, vp, i64, vp],
     }
@@ -474,6 +476,65 @@ def skinny_qkv_rope_store(x: torch.Tensor, qkv_weight: torch.Tensor, bias: Optio
            "skinny_qkv_rope_store")
     _count()
     return q
+
+
+# ------------------------------------------------------------------------------------------
+# Products for many tokens on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+TC_MIN_TOKENS = 128
+
+
+def tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] >= TC_MIN_TOKENS
+            and x.shape[1] % 8 == 0 and x.shape[1] >= 64 and weight.shape[0] % 16 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.is_contiguous() and weight.shape[1] == x.shape[1])
+
+
+def tc_status() -> int:
+    """0, or 1 when a tcgen05 kernel gave up waiting on a barrier since the library was loaded."""
+    out = ctypes.c_int(0)
+    library().pico_tc_status(ctypes.addressof(out))
+    return out.value
+
+
+def tc_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """x [M, K] times weight[N, K] transposed on the tcgen05 tensor cores; bfloat16 out."""
+    _cuda(x, weight)
+    if not tc_takes(x, weight):
+        raise KernelError("tc_linear: needs bfloat16, at least 128 tokens, K a multiple of 8, N a multiple of 16")
+    M, K = x.shape
+    N = weight.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), None, M, N, K, 0, _stream()),
+           "gemm_tcgen05")
+    _count()
+    return out
+
+
+def tc_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual [M, N] float32 += x [M, K] times weight[N, K] transposed."""
+    _cuda(x, weight, residual)
+    M, K = x.shape
+    N = weight.shape[0]
+    if not tc_takes(x, weight) or residual.dtype != torch.float32 or residual.shape != (M, N) \
+            or not residual.is_contiguous():
+        raise KernelError("tc_linear_residual: sizes not taken")
+    _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(weight), None, _ptr(residual), M, N, K, 1,
+                                       _stream()), "gemm_tcgen05 (residual)")
+    _count()
+
+
+def tc_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+    """silu(x wg^T) * (x wu^T) for gate_up_weight = [wg; wu]; returns [M, I] bfloat16."""
+    _cuda(x, gate_up_weight)
+    if not tc_takes(x, gate_up_weight):
+        raise KernelError("tc_gate_up_swiglu: sizes not taken")
+    M, K = x.shape
+    I = gate_up_weight.shape[0] // 2
+    out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
+    _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(gate_up_weight), _ptr(out), None, M, 2 * I, K, 2,
+                                       _stream()), "gemm_tcgen05 (swiglu)")
+    _count()
+    return out
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -163,6 +163,10 @@ def make_kv_tensor_map(pages):
     return None
 
 
+def tc_takes(x, weight):
+    return False
+
+
 def linear(x, weight, out=None):
     y = (x.float() @ weight.float().t()).to(x.dtype)
     if out is not None:
@@ -194,7 +198,7 @@ def sample(logits, temperature, top_p, uniform, out):
 
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
-         "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
+         "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "tc_takes", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
          "linear", "logits_linear", "sample"]
 
