@@ -132,6 +132,36 @@ def test_greedy_generation_through_the_entry_point(dtype, tmp_path):
     assert all(g.pool.in_use == 0 for g in llm.cache.groups)
 
 
+def test_a_folder_stored_in_32_bit_served_in_bfloat16(tmp_path):
+    """Matrices stored in float32 stay float32 (their products run in float32); the rest of the
+    bfloat16 path is as usual."""
+    from pico_vllm_b200.config import EngineConfig
+    from pico_vllm_b200.engine import make_runner
+    name = "c"
+    cfg = helpers.tiny_config(name)
+    helpers.write_tiny_model(name, tmp_path, dtype="float32")
+    runner = make_runner(str(tmp_path), EngineConfig(dtype="bfloat16", page_size=4, max_cache_tokens=256,
+                                                     max_num_seqs=2, device=DEV), poison_freed=True)
+    assert runner.model.blocks[0].mixer.qkv_weight.dtype == torch.float32
+    reqs = {"x": helpers.random_ids(150, cfg.vocab_size, 3)}
+    steps = helpers.trace_portions(reqs, (130, 2, 1, 17))
+    tensors = helpers.tiny_tensors(name, torch.float32)
+    want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
+    for i, (g, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+        helpers.assert_close_logits(g, w, REL["bfloat16"], f"step {i}")
+
+
+def test_command_line_generates(tmp_path, capsys):
+    from pico_vllm_b200.cli import main
+    helpers.write_tiny_model("a", tmp_path, dtype="bfloat16")
+    rc = main(["run", "--model", str(tmp_path), "--prompt-ids", "5,17,3", "--prompt-ids", "9,9", "--max-new-tokens", "4",
+               "--temperature", "0", "--num-gpu-blocks", "32", "--ignore-eos"])
+    assert rc == 0
+    lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("[")]
+    assert len(lines) == 2
+    assert sorted(len(l.split("] ")[1].split()) for l in lines) == [2 + 4, 3 + 4]
+
+
 def test_sampling_through_the_entry_point_is_reproducible(tmp_path):
     from pico_vllm_b200 import LLM, SamplingParams
     helpers.write_tiny_model("a", tmp_path, dtype="float32")
