@@ -66,6 +66,9 @@ def library():
                                   f32, i32, vp],
         "pico_paged_prefill_tma": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
         "pico_tma_status": [vp],
+        "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32],
+        "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
+        "pico_tca_status": [vp],
         "pico_gemm_tcgen05": [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp],
         "pico_tc_status": [vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
@@ -273,6 +276,28 @@ def make_kv_tensor_map(pages: torch.Tensor):
     return (buf, aligned)
 
 
+def make_kv_tensor_map_2d(pages: torch.Tensor):
+    """Like :func:`make_kv_tensor_map`, with boxes of [page_size rows, 64 dims]: the operand layout of
+    the tcgen05 prefill attention kernel.  None when the sizes are not taken."""
+    if not pages.is_cuda or pages.dtype != torch.bfloat16 or not pages.is_contiguous() or pages.dim() != 4:
+        return None
+    n_pages, nkv, ps, hd = pages.shape
+    if hd not in (64, 128) or ps not in (8, 16, 32, 64):
+        return None
+    buf = (ctypes.c_ubyte * 192)()
+    aligned = (ctypes.addressof(buf) + 63) & ~63
+    if library().pico_make_kv_tensor_map_2d(aligned, pages.data_ptr(), n_pages * nkv * ps, hd, ps) != 0:
+        return None
+    return (buf, aligned)
+
+
+def tca_status() -> int:
+    """0, or 1 when the tcgen05 attention kernel gave up waiting on a barrier since the library was loaded."""
+    out = ctypes.c_int(0)
+    library().pico_tca_status(ctypes.addressof(out))
+    return out.value
+
+
 def tma_status() -> int:
     """0, or 1 when a kernel gave up waiting for a TMA copy since the library was loaded."""
     out = ctypes.c_int(0)
@@ -286,14 +311,15 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
                         max_prefill_q: int, decode_tokens: Optional[torch.Tensor], n_decode_tokens: int,
                         n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
                         scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
-                        k_map=None, v_map=None) -> torch.Tensor:
+                        k_map=None, v_map=None, k_map2d=None, v_map2d=None) -> torch.Tensor:
     """The same attention as :func:`paged_attention` for bfloat16 on tensor cores, in two launches:
     segments that bring two or more tokens (``prefill_segs`` int32 [n_prefill_segs], None = all
     segments; ``cu_q`` int32 [segments + 1]; ``max_prefill_q`` their longest) and single tokens
     (``decode_tokens`` int32 [n_decode_tokens], None = every token of the batch) whose key range is
     cut into ``n_splits`` parts.  Every token of the batch must be in exactly one of the two.
     With ``k_map`` / ``v_map`` (from :func:`make_kv_tensor_map` over these same pages) the single
-    tokens run in the kernel that brings pages in by TMA."""
+    tokens run in the kernel that brings pages in by TMA; with ``k_map2d`` / ``v_map2d`` (from
+    :func:`make_kv_tensor_map_2d`) the portions run on the tcgen05 tensor cores."""
     _cuda(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs, decode_tokens, scratch)
     T = q.shape[0]
     if not mma_attention_takes(q.dtype, n_heads, n_kv_heads, head_dim):
@@ -313,7 +339,14 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     lib = library()
     win = int(window) if window else 0
     use_tma = k_map is not None and v_map is not None
-    if n_prefill_segs > 0 and use_tma and n_heads // n_kv_heads <= 64:
+    if n_prefill_segs > 0 and k_map2d is not None and v_map2d is not None:
+        _check(lib.pico_paged_prefill_tcgen05(k_map2d[1], v_map2d[1], _ptr(q), q.stride(0), _ptr(out),
+                                              _ptr(prefill_segs), n_prefill_segs, _ptr(cu_q), max_prefill_q,
+                                              _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
+                                              n_kv_heads, head_dim, page_size, win, float(scale), _stream()),
+               f"paged_prefill_tcgen05 (head_dim {head_dim})")
+        _count()
+    elif n_prefill_segs > 0 and use_tma and n_heads // n_kv_heads <= 64:
         _check(lib.pico_paged_prefill_tma(k_map[1], v_map[1], _ptr(q), q.stride(0), _ptr(out), _ptr(prefill_segs),
                                           n_prefill_segs, _ptr(cu_q), max_prefill_q, _ptr(positions),
                                           _ptr(block_table), block_table.stride(0), n_heads, n_kv_heads, head_dim,

@@ -77,6 +77,8 @@ class CacheView:
     state: Optional[torch.Tensor] = None
     k_map: object = None       # TMA tensor maps over k and v (ops.make_kv_tensor_map), or None
     v_map: object = None
+    k_map2d: object = None     # the same pages in [page_size, 64]-boxes (ops.make_kv_tensor_map_2d), or None
+    v_map2d: object = None
 
 
 class Part:

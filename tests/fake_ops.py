@@ -104,7 +104,8 @@ def mma_attention_takes(dtype, n_heads, n_kv_heads, head_dim):
 
 def paged_attention_mma(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs,
                         n_prefill_segs, max_prefill_q, decode_tokens, n_decode_tokens, n_heads, n_kv_heads, head_dim,
-                        page_size, window, scale, n_splits=1, scratch=None, k_map=None, v_map=None):
+                        page_size, window, scale, n_splits=1, scratch=None, k_map=None, v_map=None, k_map2d=None,
+                        v_map2d=None):
     return paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads, head_dim,
                            page_size, window, scale)
 
@@ -163,6 +164,10 @@ def make_kv_tensor_map(pages):
     return None
 
 
+def make_kv_tensor_map_2d(pages):
+    return None
+
+
 def tc_takes(x, weight):
     return False
 
@@ -198,7 +203,7 @@ def sample(logits, temperature, top_p, uniform, out):
 
 
 NAMES = ["embedding", "add_rmsnorm", "swiglu", "rope_store", "attention_scratch_floats", "paged_attention",
-         "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "tc_takes", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
+         "mma_attention_takes", "paged_attention_mma", "make_kv_tensor_map", "make_kv_tensor_map_2d", "tc_takes", "skinny_takes", "skinny_norm_takes", "skinny_linear", "skinny_linear_residual",
          "skinny_gate_up_swiglu", "skinny_qkv_rope_store",
          "linear", "logits_linear", "sample"]
 

@@ -99,7 +99,7 @@ def test_rope_store(dtype, nh, nkv, hd, ps, rot):
 
 
 def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, seed=0, spike=False, mma=False,
-                    tma=False, poison=False):
+                    tma=False, poison=False, tc=False):
     """Segments with kv lengths seg_lens, of which the last q_lens are this step's queries."""
     from pico_vllm_b200 import ops
     g = gen(20 + seed)
@@ -152,12 +152,17 @@ def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, se
         maps = (ops.make_kv_tensor_map(kd), ops.make_kv_tensor_map(vd)) if tma else (None, None)
         if tma:
             assert maps[0] is not None and maps[1] is not None
+        if tc:
+            maps = maps + (ops.make_kv_tensor_map_2d(kd), ops.make_kv_tensor_map_2d(vd))
+            assert maps[2] is not None and maps[3] is not None
         ops.paged_attention_mma(q.to(DEV), kd, vd, out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
                                 cu.to(DEV), pf.to(DEV), len(pf), max([n for n in q_lens if n > 1], default=0),
                                 dec.to(DEV), len(dec), nh, nkv, hd, ps, window, scale, splits, scratch, *maps)
         if tma:
             torch.cuda.synchronize()
             assert ops.tma_status() == 0
+        if tc:
+            assert ops.tca_status() == 0
     else:
         ops.paged_attention(q.to(DEV), k.to(DEV), v.to(DEV), out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
                             nh, nkv, hd, ps, window, scale, splits, scratch)
@@ -235,6 +240,23 @@ def test_tma_attention_mixed_segments(nh, nkv, hd, ps, window):
     got, want = _attention_case(torch.bfloat16, nh, nkv, hd, ps, window, seg_lens=[300, 133, 9, 1, 70, 2, 64, 190],
                                 q_lens=[257, 1, 2, 1, 33, 2, 1, 64], splits=1, mma=True, tma=True, poison=True)
     assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(6, 2, 64, 16), (12, 2, 128, 16), (7, 1, 128, 8), (16, 1, 64, 32), (4, 4, 128, 64),
+                                          (28, 4, 128, 16), (3, 3, 64, 8)])
+@pytest.mark.parametrize("window", [None, 24, 200])
+def test_tcgen05_attention_mixed_segments(nh, nkv, hd, ps, window):
+    got, want = _attention_case(torch.bfloat16, nh, nkv, hd, ps, window, seg_lens=[300, 133, 9, 1, 70, 2, 64, 190, 1000],
+                                q_lens=[257, 1, 2, 1, 33, 2, 1, 64, 700], splits=1, mma=True, tma=True, poison=True, tc=True)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("window,q_lens", [(None, [200, 150]), (64, [200, 150]), (None, [2, 300]), (100, [517, 64])])
+def test_tcgen05_prefill_far_key_and_window_edge(window, q_lens):
+    got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=q_lens, splits=1,
+                                seed=5, spike=True, mma=True, tma=True, poison=True, tc=True)
     assert torch.allclose(got, want, **MMA_TOL)
 
 
