@@ -167,7 +167,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     pdl_wait();
     const int seg = seg_list ? seg_list[blockIdx.z] : blockIdx.z;
     const int q0 = cu_q[seg], qlen = cu_q[seg + 1] - q0;
-    const int tok0 = blockIdx.x * tpt;
+    // the tiles with the most keys (the last tokens) are launched first, so that they do not form the tail
+    const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * tpt;
     const bool active = tok0 < qlen;                         // uniform for the block
     const int ntok = active ? min(tpt, qlen - tok0) : 0;
     const int pos0 = active ? positions[q0] + tok0 : 0;      // position of the tile's first token
