@@ -320,6 +320,25 @@ def run_micro(args):
             tc = graph_time([lambda: torch.mm(x, w.t())] * 8)
             out[f"tcgen05_{name}"] = {"us": round(t, 1), "tflops": round(fl / t / 1e6), "cublas_us": round(tc, 1),
                                       "fused": "swiglu" if name == "gate_up" else None}
+        # causal attention of one prompt of M tokens over its own pages
+        nh, nkv, hd, ps = 12, 2, 128, 16
+        blocks = (M + ps - 1) // ps
+        k = torch.randn(blocks, nkv, ps, hd, device=dev).bfloat16()
+        v = torch.randn(blocks, nkv, ps, hd, device=dev).bfloat16()
+        table = torch.randperm(blocks, device=dev).int().view(1, blocks).contiguous()
+        q = torch.randn(M, (nh + 2 * nkv) * hd, device=dev).bfloat16()
+        o = torch.empty(M, nh * hd, device=dev).bfloat16()
+        seg = torch.zeros(M, device=dev).int()
+        pos = torch.arange(M, device=dev).int()
+        cu = torch.tensor([0, M], device=dev).int()
+        pf = torch.zeros(1, device=dev).int()
+        dec = torch.zeros(0, device=dev).int()
+        maps = (ops.make_kv_tensor_map(k), ops.make_kv_tensor_map(v), ops.make_kv_tensor_map_2d(k),
+                ops.make_kv_tensor_map_2d(v, values=True))
+        t = graph_time([lambda: ops.paged_attention_mma(q, k, v, o, seg, pos, table, cu, pf, 1, M, dec, 0, nh, nkv, hd,
+                                                        ps, None, hd ** -0.5, 1, None, *maps)] * 8)
+        fl = 2.0 * 2 * nh * hd * M * (M + 1) / 2          # the visible (query, key) pairs only
+        out["prefill_attention"] = {"us": round(t, 1), "tflops_causal": round(fl / t / 1e6)}
         print(json.dumps(out))
         return 0
     nh, nkv, hd, ps, L, ctx = 12, 2, 128, 16, 24, args.context

@@ -221,7 +221,7 @@ class CacheManager:
                 if g.k is not None and g.k.is_cuda and g.k.dtype == torch.bfloat16:
                     from .. import ops
                     view.k_map, view.v_map = ops.make_kv_tensor_map(view.k), ops.make_kv_tensor_map(view.v)
-                    view.k_map2d, view.v_map2d = ops.make_kv_tensor_map_2d(view.k), ops.make_kv_tensor_map_2d(view.v)
+                    view.k_map2d, view.v_map2d = ops.make_kv_tensor_map_2d(view.k), ops.make_kv_tensor_map_2d(view.v, values=True)
                 out.append(view)
             else:
                 out.append(CacheView(state=self.states.get(eid)))

@@ -2,16 +2,25 @@
 //
 // A block takes 128 rows of queries - 128 / g tokens of one segment times the g query heads that
 // share a key/value head - and walks the visible cache positions 64 at a time:
-//   warp 0      issues the TMA copies of the pages of a tile (keys and values, [page rows, 64 dims]
-//               boxes in the 128-byte swizzle, several lanes issuing in parallel);
-//   warp 1      one lane issues tcgen05.mma: S = Q K^T (M 128, N 64, accumulator S in tensor memory)
-//               and, once the probabilities are ready, O += P V (M 128, N head_dim, V as an MN-major
-//               operand, accumulator O in tensor memory); tcgen05.commit signals mbarriers;
-//   warps 2-5   softmax: thread = row.  tcgen05.ld of the row's 64 scores, mask, running max and sum in
-//               float32 (exp2 on scores scaled to log2 units), probabilities as bfloat16 into shared
-//               memory in the operand layout; the O accumulator is rescaled in tensor memory
-//               (tcgen05.ld / st) only when a row's maximum has grown by more than 2^8 since the value in
-//               use, which is exact because the same maximum is used for the sum; at the end O / sum.
+//   warps 0, 13   issue the TMA copies of the pages of a tile, lane = box: warp 0 the keys ([page rows, 64
+//               dims] boxes, one per page and 64-dim block), warp 13 the values (one box per page with all
+//               its 64-dim blocks), 128-byte swizzle, separate rings for keys and values: a key stage is
+//               free once S = Q K^T has read it, a value stage once O += P V has;
+//   warps 1, 10-12  one lane each issues tcgen05.mma: S = Q K^T (M 128, N 64, Q and K from shared memory,
+//               accumulator S in tensor memory) for pipeline 0 (warp 1) and 1 (warp 10); O += P V (M 128,
+//               N head_dim, P read from tensor memory, V from shared memory as an MN-major operand,
+//               accumulator O in tensor memory) for pipeline 0 (warp 11) and 1 (warp 12).  A tcgen05.mma
+//               costs its issuing thread about a hundred clocks whatever its size (measured), so one
+//               issuing thread would be the bottleneck; tcgen05.commit signals mbarriers;
+//   warps 2-9   softmax, two groups of four warps: thread = row.  tcgen05.ld of the row's 64 scores,
+//               mask, running max and sum in float32 (exp2 on scores scaled to log2 units, packed
+//               two-lane fma / add), probabilities as bfloat16 pairs back into tensor memory
+//               (tcgen05.st); the O accumulator is rescaled in tensor memory only when a row's maximum
+//               has grown by more than 2^8 since the value in use, which is exact because the same
+//               maximum is used for the sum.
+// Even tiles go through pipeline 0 (its own S, P, O columns and softmax group), odd tiles through
+// pipeline 1, so that one tile's softmax runs beside the other's and beside the products; at the end
+// the two partial results (O, maximum, sum) are merged and divided by the sum.
 // Rules restated from the reference: query head j reads key/value head j / g
 // (pico_vllm/kernels/attention.py:139); scores * hd^-1/2 (attention.py:231); key n visible to the
 // query at position p iff n <= p (attention.py:193-198) - and n > p - window with a window; online
@@ -22,13 +31,14 @@
 
 #define TCA_BM 128
 #define TCA_BN 64
-#define TCA_THREADS 192
-#define TCA_STAGES 3
-#define TCA_WAIT_LIMIT (1 << 20)
+#define TCA_THREADS 448
+#define TCA_STAGES 4
+#define TCA_WAIT_LIMIT (1 << 14)     // polls of a barrier (some microseconds each) before a thread gives up
 #define TCA_TABLE_CACHE 1024
 #define TCA_RESCALE_AT 8.0f     // log2 units: rescale the accumulator when the maximum grew by more than this
 
 __device__ int g_tca_status = 0;
+
 PICO_API int pico_tca_status(int* out) {
     return (int)cudaMemcpyFromSymbol(out, g_tca_status, sizeof(int), 0, cudaMemcpyDeviceToHost);
 }
@@ -61,19 +71,25 @@ __device__ __forceinline__ void tca_tma_2d(void* dst, const CUtensorMap* map, in
         ::"r"(tca_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(tca_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tca_tma_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+        ::"r"(tca_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(tca_u32(bar))
+        : "memory");
+}
 // K-major operand [rows][64 bf16] in the 128-byte swizzle (rows 128 bytes, 8-row groups 1024 bytes apart)
 __device__ __forceinline__ uint64_t tca_desc_k(uint32_t tile, int k16) {
     const uint32_t addr = tile + k16 * 32;
     return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
            ((uint64_t)2 << 61);
 }
-// MN-major operand: values [keys][head dims], head dims contiguous, stored as blocks of [64 keys][64 dims]
-// (128-byte rows, 128-byte swizzle): 8-key groups 1024 bytes apart (stride byte offset), 64-dim blocks
-// `block_bytes` apart (leading byte offset).  k16 selects 16 keys.
-__device__ __forceinline__ uint64_t tca_desc_mn(uint32_t tile, int k16, uint32_t block_bytes) {
-    const uint32_t addr = tile + k16 * 16 * 128;
-    return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((block_bytes >> 4) & 0x3fff) << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+// MN-major operand: values [keys][head dims], head dims contiguous.  A value tile is stored page by page,
+// each page as its 64-dim blocks one after the other ([block][page rows][128 bytes], 128-byte swizzle):
+// `addr` is the first of 16 keys, 64-dim blocks are `block_bytes` apart (leading byte offset) and the two
+// groups of 8 keys `group_bytes` apart (stride byte offset: 1024 inside a page).
+__device__ __forceinline__ uint64_t tca_desc_mn(uint32_t addr, uint32_t block_bytes, uint32_t group_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((block_bytes >> 4) & 0x3fff) << 16) |
+           ((uint64_t)((group_bytes >> 4) & 0x3fff) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 __device__ __forceinline__ void tca_mma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
     const uint32_t zero = 0;
@@ -114,7 +130,46 @@ __device__ __forceinline__ float tca_exp2(float x) {
     return y;
 }
 __device__ __forceinline__ void tca_fence_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ void tca_sm_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tca_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    const uint32_t zero = 0;       // the a operand is read from tensor memory
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(acc), "r"(zero) : "memory");
+}
+__device__ __forceinline__ float tca_max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
+// two float32 lanes in one 64-bit register: the packed forms of fma and add halve the instruction count
+__device__ __forceinline__ uint64_t tca_pack(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void tca_unpack(uint64_t r, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ uint64_t tca_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t tca_add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ void tca_softmax_sync() { asm volatile("bar.sync 2, 256;\n" ::: "memory"); }
+
+// Tensor-memory columns of a block (512 allocated): scores of the two pipelines, their probabilities
+// (bfloat16 pairs, the a operand of p.v), their output accumulators.
+#define TCA_COL_S 0
+#define TCA_COL_P 128
+#define TCA_COL_O 192
 
 template <int HD>      // head size, a multiple of 64 up to 128
 __global__ void __launch_bounds__(TCA_THREADS)
@@ -131,17 +186,20 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     constexpr int QSUB = TCA_BM * 128;                       // bytes of one [128 rows][64 dims] block of Q
     unsigned char* smem = tca_dyn + ((1024u - (tca_u32(tca_dyn) & 1023u)) & 1023u);
     unsigned char* q_s = smem;                               // [NH][128 rows][128 B]
-    unsigned char* p_s = q_s + NH * QSUB;                    // [128 rows][128 B]: probabilities of 64 keys
-    unsigned char* kv_s = p_s + QSUB;                        // [stages][K tile | V tile]
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(kv_s + TCA_STAGES * 2 * KV_BYTES);
-    uint64_t* kv_empty = kv_full + TCA_STAGES;
-    uint64_t* s_full = kv_empty + TCA_STAGES;                // the scores of a tile are in tensor memory
-    uint64_t* s_empty = s_full + 1;                          // the softmax warps have read them
-    uint64_t* p_full = s_empty + 1;                          // the probabilities are in shared memory (and O is rescaled)
-    uint64_t* pv_done = p_full + 1;                          // the p.v products of a tile are done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    unsigned char* k_s = q_s + NH * QSUB;                    // [stages] K tiles: a stage is free once S = Q K^T has read it
+    unsigned char* v_s = k_s + TCA_STAGES * KV_BYTES;        // [stages] V tiles: free once O += P V has read it, two tiles later
+    uint64_t* k_full = reinterpret_cast<uint64_t*>(v_s + TCA_STAGES * KV_BYTES);
+    uint64_t* k_empty = k_full + TCA_STAGES;
+    uint64_t* v_full = k_empty + TCA_STAGES;
+    uint64_t* v_empty = v_full + TCA_STAGES;
+    uint64_t* s_full = v_empty + TCA_STAGES;                 // [2] the scores of a tile are in tensor memory
+    uint64_t* s_empty = s_full + 2;                          // [2] the softmax warps have read them
+    uint64_t* p_full = s_empty + 2;                          // [2] the probabilities are in tensor memory (and O is rescaled)
+    uint64_t* pv_done = p_full + 2;                          // [2] the p.v products of a tile are done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
     volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* tbl_s = const_cast<int*>(abort_s) + 2;              // [TCA_TABLE_CACHE]
+    float2* ml_s = reinterpret_cast<float2*>(const_cast<int*>(abort_s) + 3);   // [2][128] maximum in use and sum of a row
+    int* tbl_s = reinterpret_cast<int*>(ml_s + 2 * TCA_BM);  // [TCA_TABLE_CACHE]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = nh / nkv;
     const int tpt = TCA_BM / g;
@@ -149,19 +207,23 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TCA_STAGES; ++s) {
-            tca_mbar_init(kv_full + s, 1);
-            tca_mbar_init(kv_empty + s, 1);
+            tca_mbar_init(k_full + s, 1);
+            tca_mbar_init(k_empty + s, 1);
+            tca_mbar_init(v_full + s, 1);
+            tca_mbar_init(v_empty + s, 1);
         }
-        tca_mbar_init(s_full, 1);
-        tca_mbar_init(s_empty, 4);
-        tca_mbar_init(p_full, 4);
-        tca_mbar_init(pv_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            tca_mbar_init(s_full + i, 1);
+            tca_mbar_init(s_empty + i, 4);
+            tca_mbar_init(p_full + i, 4);
+            tca_mbar_init(pv_done + i, 1);
+        }
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         tca_fence_async();
     }
-    if (warp == 1) {       // tensor memory: 64 columns of scores + HD columns of output (256 allocated)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tca_u32(tmem_slot)), "r"(256));
+    if (warp == 1) {       // all 512 columns of tensor memory (448 used at head size 128)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tca_u32(tmem_slot)), "r"(512));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     pdl_wait();
@@ -199,70 +261,102 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + TCA_BN;
 
-    if (warp == 0) {
-        // ---------------------------------------------------------------- producer: lane 2*(pg*NH+h) + {0: K, 1: V}
+    if (warp == 0 || warp == 13) {
+        // ---------------------------------------------------------------- producers: warp 0 copies keys, warp 13 values
+        // keys: one box per (page, 64-dim block), [block][64 keys][128 bytes]; values: one box per page with
+        // all its 64-dim blocks, [page][block][page rows][128 bytes].  Lane = box.
+        const int kv = warp == 13;
+        const int jobs = kv ? ppt : ppt * NH;
+        const int h = kv ? 0 : lane % NH, pg = kv ? lane : lane / NH;
+        const CUtensorMap* map = kv ? &v_map : &k_map;
+        unsigned char* ring = (kv ? v_s : k_s) + (kv ? pg * page_size * (NH * 128) : h * SUB + pg * page_size * 128);
+        uint64_t* full_b = kv ? v_full : k_full;
+        uint64_t* empty_b = kv ? v_empty : k_empty;
+        const int row_mul = nkv * page_size, row_add = kh * page_size;
         for (int it = 0; it < ntiles; ++it) {
             const int s = it % TCA_STAGES;
-            if (it >= TCA_STAGES && !tca_wait(kv_empty + s, ((it / TCA_STAGES) - 1) & 1)) {
+            if (it >= TCA_STAGES && !tca_wait(empty_b + s, ((it / TCA_STAGES) - 1) & 1)) {
                 g_tca_status = 1;
                 *abort_s = 1;
             }
-            __syncwarp();
-            if (*abort_s) break;
+            if (__any_sync(0xffffffffu, *abort_s != 0)) break;
             const int n0 = (t_begin + it) * TCA_BN;
-            unsigned char* kt = kv_s + (size_t)s * 2 * KV_BYTES;
-            int first = 0, last = ppt;        // pages wholly outside [lo, hi) are not copied
-            while (first < last && n0 + (first + 1) * page_size <= lo) ++first;
-            while (last > first && n0 + (last - 1) * page_size >= hi) --last;
-            if (lane == 0) tca_expect_tx(kv_full + s, (uint32_t)((last - first) * page_size * HD * 2 * 2));
-            __syncwarp();
-            for (int job = lane; job < ppt * NH * 2; job += 32) {
-                const int kv = job & 1, h = (job >> 1) % NH, pg = (job >> 1) / NH;
-                if (pg >= first && pg < last) {
-                    const int e = it * ppt + pg;
-                    const int page = e < TCA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
-                    const int row = (page * nkv + kh) * page_size;
-                    tca_tma_2d(kt + kv * KV_BYTES + h * SUB + pg * page_size * 128, kv ? &v_map : &k_map, h * 64, row,
-                               kv_full + s);
-                }
+            int first = 0, last = ppt;            // pages wholly outside [lo, hi) are not copied
+            if (n0 < lo || n0 + TCA_BN > hi) {
+                while (first < last && n0 + (first + 1) * page_size <= lo) ++first;
+                while (last > first && n0 + (last - 1) * page_size >= hi) --last;
             }
+            if (lane == 0) tca_expect_tx(full_b + s, (uint32_t)((last - first) * page_size * HD * 2));
+            __syncwarp();
+            if (lane < jobs && pg >= first && pg < last) {
+                const int e = it * ppt + pg;
+                const int page = e < TCA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
+                const int row = page * row_mul + row_add;
+                if (kv) tca_tma_3d(ring + (size_t)s * KV_BYTES, map, 0, row, 0, full_b + s);
+                else tca_tma_2d(ring + (size_t)s * KV_BYTES, map, h * 64, row, full_b + s);
+            }
+            __syncwarp();
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || (warp >= 10 && warp <= 12)) {
         // ---------------------------------------------------------------- tensor-core issue
-        if (lane == 0 && ntiles > 0) {
+        // Two pipelines: even tiles use S, P, O number 0, odd tiles number 1, so that one tile's softmax
+        // runs beside the other's; the two partial outputs are added at the end.  A tcgen05.mma costs its
+        // issuing thread about a hundred clocks whatever its size, so four threads issue: warps 1 and 10
+        // the S = Q K^T products of pipelines 0 and 1, warps 11 and 12 their O += P V products.
+        const int pipe = (warp == 1 || warp == 11) ? 0 : 1;
+        const bool is_pv = warp >= 11;
+        if (lane == 0 && ntiles > pipe) {
             // float32 accumulate, bfloat16 operands; S: N = 64, both K-major; O: N = HD, b MN-major
             const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TCA_BN >> 3) << 17) | ((uint32_t)(TCA_BM >> 4) << 24);
             const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(TCA_BM >> 4) << 24);
-            const uint32_t qa = tca_u32(q_s), pa = tca_u32(p_s);
-            auto issue_qk = [&](int it) -> bool {
-                const int s = it % TCA_STAGES;
-                if (!tca_wait(kv_full + s, (it / TCA_STAGES) & 1)) return false;
-                if (it > 0 && !tca_wait(s_empty, (it - 1) & 1)) return false;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t kt = tca_u32(kv_s + (size_t)s * 2 * KV_BYTES);
+            bool ok = true;
+            // every descriptor is made once: per tile only the stage's offset (in 16-byte units) is added
+            if (!is_pv) {
+                uint64_t q_desc[NH * 4], k_desc[NH * 4];
+                const uint32_t qa = tca_u32(q_s), k0 = tca_u32(k_s);
 #pragma unroll
                 for (int h = 0; h < NH; ++h)
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16)
-                        tca_mma(tmem_s, tca_desc_k(qa + h * QSUB, k16), tca_desc_k(kt + h * SUB, k16), idesc_s, (h | k16) ? 1u : 0u);
-                tca_commit(s_full);
-                return true;
-            };
-            bool ok = issue_qk(0);
-            for (int it = 0; ok && it < ntiles; ++it) {
-                if (it + 1 < ntiles) ok = issue_qk(it + 1);           // the next tile's scores while this tile's softmax runs
-                if (!ok) break;
-                if (!tca_wait(p_full, it & 1)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const int s = it % TCA_STAGES;
-                const uint32_t vt = tca_u32(kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES);
+                    for (int k16 = 0; k16 < 4; ++k16) {
+                        q_desc[h * 4 + k16] = tca_desc_k(qa + h * QSUB, k16);
+                        k_desc[h * 4 + k16] = tca_desc_k(k0 + h * SUB, k16);
+                    }
+                const uint32_t ts = tmem_base + TCA_COL_S + pipe * TCA_BN;
+                int j = 0;
+                for (int it = pipe; it < ntiles; it += 2, ++j) {
+                    const int s = it % TCA_STAGES;
+                    if (!tca_wait(k_full + s, (it / TCA_STAGES) & 1) || (j > 0 && !tca_wait(s_empty + pipe, (j - 1) & 1))) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint64_t stage = (uint64_t)(s * (KV_BYTES >> 4));
 #pragma unroll
-                for (int k16 = 0; k16 < 4; ++k16)
-                    tca_mma(tmem_o, tca_desc_k(pa, k16), tca_desc_mn(vt, k16, SUB), idesc_o, (it | k16) ? 1u : 0u);
-                tca_commit(kv_empty + s);      // keys and values of the stage have been read
-                tca_commit(pv_done);           // P may be overwritten, O holds this tile
+                    for (int i = 0; i < NH * 4; ++i) tca_mma(ts, q_desc[i], k_desc[i] + stage, idesc_s, i ? 1u : 0u);
+                    tca_commit(k_empty + s);           // the keys of the stage have been read
+                    tca_commit(s_full + pipe);
+                }
+            } else {
+                uint64_t v_desc[4];
+                // 16 keys per product: they lie in one page (two pages of 8 rows), 64-dim blocks page_size rows apart
+                const uint32_t v0 = tca_u32(v_s), page_bytes = (uint32_t)(page_size * NH * 128);
+                const uint32_t group_bytes = page_size >= 16 ? 1024u : page_bytes;
+#pragma unroll
+                for (int k16 = 0; k16 < 4; ++k16) {
+                    const int key = k16 * 16;
+                    v_desc[k16] = tca_desc_mn(v0 + (uint32_t)(key / page_size) * page_bytes + (uint32_t)(key % page_size) * 128u,
+                                              (uint32_t)page_size * 128u, group_bytes);
+                }
+                const uint32_t tp = tmem_base + TCA_COL_P + pipe * (TCA_BN / 2), to = tmem_base + TCA_COL_O + pipe * HD;
+                int j = 0;
+                for (int it = pipe; it < ntiles; it += 2, ++j) {
+                    const int s = it % TCA_STAGES;
+                    if (!tca_wait(v_full + s, (it / TCA_STAGES) & 1) || !tca_wait(p_full + pipe, j & 1)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint64_t stage = (uint64_t)(s * (KV_BYTES >> 4));
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16) tca_mma_ts(to, tp + k16 * 8, v_desc[k16] + stage, idesc_o, (j | k16) ? 1u : 0u);
+                    tca_commit(v_empty + s);           // the values of the stage have been read
+                    tca_commit(pv_done + pipe);        // P may be overwritten, O holds this tile
+                }
             }
             if (!ok) {
                 g_tca_status = 1;
@@ -271,6 +365,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         }
     } else {
         // ---------------------------------------------------------------- softmax warps: thread = row
+        const int pipe = (warp - 2) >> 2;                    // warps 2-5: even tiles, warps 6-9: odd tiles
         const int qtr = warp & 3;
         const int r = qtr * 32 + lane;                       // row of the tile = tensor-memory lane
         const int tok = r / g, head = r - tok * g;
@@ -278,126 +373,158 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const int row_pos = row_ok ? pos0 + tok : -1;
         const int row_lo = (window > 0 && row_pos + 1 > window) ? row_pos + 1 - window : 0;
         const uint32_t lane_off = (uint32_t)(qtr * 32) << 16;
+        const uint32_t tmem_s = tmem_base + TCA_COL_S + pipe * TCA_BN + lane_off;
+        const uint32_t tmem_p = tmem_base + TCA_COL_P + pipe * (TCA_BN / 2) + lane_off;
+        const uint32_t tmem_o = tmem_base + TCA_COL_O + pipe * HD + lane_off;
         float m_use = -INFINITY, l = 0.f;                    // maximum in use (log2 units), running sum
         bool dead = false;
-        for (int it = 0; it < ntiles; ++it) {
+        const uint64_t scale2 = tca_pack(scale_log2, scale_log2);
+        int j = 0;
+        for (int it = pipe; it < ntiles; it += 2, ++j) {
             const int n0 = (t_begin + it) * TCA_BN;
             const int s = it % TCA_STAGES;
-            if (!tca_wait(s_full, it & 1)) {
+            bool waited = tca_wait(s_full + pipe, j & 1);
+            if (!waited) {
                 g_tca_status = 1;
                 *abort_s = 1;
             }
-            if (*abort_s) { dead = true; break; }
+            if (__any_sync(0xffffffffu, !waited || *abort_s != 0)) { dead = true; break; }      // the warp leaves together
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             uint32_t sv[64];
-            tca_ld32(tmem_s + lane_off, *reinterpret_cast<uint32_t(*)[32]>(sv));
-            tca_ld32(tmem_s + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
+            tca_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(sv));
+            tca_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(sv + 32));
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) tca_arrive(s_empty);              // the next tile's scores may be written
-            const bool edge = n0 + TCA_BN - 1 > pos0 || n0 < row_lo || n0 < lo;       // some key may be hidden from some row
-            float mx = -INFINITY;
+            if (lane == 0) tca_arrive(s_empty + pipe);       // this pipeline's next scores may be written
+            if (n0 + TCA_BN - 1 > pos0 || n0 < row_lo || n0 < lo) {      // some key may be hidden from some row
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float x = __uint_as_float(sv[c]) * scale_log2;
-                if (edge) {
+                for (int c = 0; c < 64; ++c) {
                     const int n = n0 + c;
-                    if (!(n <= row_pos && n >= row_lo)) x = -INFINITY;
+                    if (!(n <= row_pos && n >= row_lo)) sv[c] = 0xff800000u;     // -inf
                 }
-                sv[c] = __float_as_uint(x);
-                mx = fmaxf(mx, x);
             }
+            // the maximum of the raw scores (the scale is positive), four chains of three-input maxima
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    mx4[i] = tca_max3(mx4[i], __uint_as_float(sv[c + 2 * i]), __uint_as_float(sv[c + 2 * i + 1]));
+            }
+            const float mx = fmaxf(tca_max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * scale_log2;
             // the maximum in use moves only when the true one has grown by more than 2^8: the same
             // value is used for the probabilities and for the sum, so the result is exact
             const bool grow = mx > m_use + TCA_RESCALE_AT;
             const float m_new = grow ? mx : m_use;
-            const float corr = (grow && m_use != -INFINITY) ? tca_exp2(m_use - m_new) : 1.0f;
             const bool need = grow && m_use != -INFINITY;    // O holds something that has to be rescaled
+            const float corr = need ? tca_exp2(m_use - m_new) : 1.0f;
             m_use = m_new;
-            const float m_sub = m_use == -INFINITY ? 0.f : m_use;
-            float sum = 0.f;
+            const float neg_m = m_use == -INFINITY ? 0.f : -m_use;
+            const uint64_t neg_m2 = tca_pack(neg_m, neg_m);
+            uint64_t sum2[2] = {0ull, 0ull};
             uint32_t pk[32];
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
-                const float p0 = tca_exp2(__uint_as_float(sv[c]) - m_sub), p1 = tca_exp2(__uint_as_float(sv[c + 1]) - m_sub);
-                sum += p0 + p1;
+                float x0, x1;
+                tca_unpack(tca_fma2(tca_pack(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, neg_m2), x0, x1);
+                const float p0 = tca_exp2(x0), p1 = tca_exp2(x1);
+                sum2[(c >> 1) & 1] = tca_add2(sum2[(c >> 1) & 1], tca_pack(p0, p1));
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                 pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h2);
             }
-            l = l * corr + sum;
-            // P and O of the tile before must have been consumed / completed
-            if (it > 0 && !tca_wait(pv_done, (it - 1) & 1)) {
+            float sa, sb;
+            tca_unpack(tca_add2(sum2[0], sum2[1]), sa, sb);
+            l = l * corr + (sa + sb);
+            // P and O of this pipeline's tile before must have been consumed / completed
+            waited = j == 0 || tca_wait(pv_done + pipe, (j - 1) & 1);
+            if (!waited) {
                 g_tca_status = 1;
                 *abort_s = 1;
             }
-            if (*abort_s) { dead = true; break; }
+            if (__any_sync(0xffffffffu, !waited || *abort_s != 0)) { dead = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             if (__any_sync(0xffffffffu, need)) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll 1
                 for (int c = 0; c < HD; c += 32) {
                     uint32_t ov[32];
-                    tca_ld32(tmem_o + lane_off + c, ov);
+                    tca_ld32(tmem_o + c, ov);
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * corr);
-                    tca_st32(tmem_o + lane_off + c, ov);
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    tca_st32(tmem_o + c, ov);
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
-            // probabilities -> shared memory, operand layout
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(p_s + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            // probabilities -> tensor memory: column i of the row holds keys 2i (low half) and 2i + 1
+            tca_st32(tmem_p, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             // value rows outside [lo, hi) may hold anything (pages given back, what lies beyond the
             // request's last token): they are cleared before the tensor core multiplies them by zero
             if (n0 < lo || n0 + TCA_BN > hi) {
-                if (!tca_wait(kv_full + s, (it / TCA_STAGES) & 1)) {
+                if (!tca_wait(v_full + s, (it / TCA_STAGES) & 1)) {
                     g_tca_status = 1;
                     *abort_s = 1;
                 }
-                unsigned char* vt = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
+                unsigned char* vt = v_s + (size_t)s * KV_BYTES;
                 const int key = r & 63;
                 const int n = n0 + key;
                 if (n < lo || n >= hi) {
                     for (int h = r >> 6; h < NH; h += 2) {
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(vt + h * SUB + key * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4*>(vt + ((key / page_size) * NH + h) * (page_size * 128) + (key % page_size) * 128 + c * 16) =
+                                make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
+                tca_fence_async();
             }
-            tca_fence_async();
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) tca_arrive(p_full);
+            if (lane == 0) tca_arrive(p_full + pipe);
         }
-        if (!dead && ntiles > 0) {
-            if (!tca_wait(pv_done, (ntiles - 1) & 1)) {
-                g_tca_status = 1;
-                *abort_s = 1;
-                dead = true;
-            }
+        // this pipeline's last p.v
+        if (!dead && j > 0 && !tca_wait(pv_done + pipe, (j - 1) & 1)) {
+            g_tca_status = 1;
+            *abort_s = 1;
         }
-        if (!dead && ntiles > 0 && !*abort_s) {
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+        ml_s[pipe * TCA_BM + r] = make_float2(m_use, l);
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        tca_softmax_sync();              // every softmax thread comes here exactly once
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (ntiles > 0 && !*abort_s) {
+            // out = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)); each pipeline's
+            // warps write half of the head's dims.  A pipeline without tiles holds nothing that may be read.
+            const bool two = ntiles > 1;
+            const float2 a = ml_s[r], b = two ? ml_s[TCA_BM + r] : make_float2(-INFINITY, 0.f);
+            const float m = fmaxf(a.x, b.x);
+            const float fa = a.x == -INFINITY ? 0.f : tca_exp2(a.x - m), fb = b.x == -INFINITY ? 0.f : tca_exp2(b.x - m);
+            const float den = a.y * fa + b.y * fb;
+            const float inv = den > 0.f ? 1.0f / den : 0.f;
+            const float wa = fa * inv, wb = fb * inv;
+            const uint32_t o_a = tmem_base + TCA_COL_O + lane_off, o_b = o_a + HD;
             bf16* dst = out + ((size_t)(q0 + tok0 + (row_ok ? tok : 0)) * nh + kh * g + head) * HD;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t ov[32];
-                tca_ld32(tmem_o + lane_off + c, ov);
+            for (int c = pipe * (HD / 2); c < (pipe + 1) * (HD / 2); c += 32) {
+                uint32_t ov[32], ow[32];
+                tca_ld32(o_a + c, ov);
+                if (two) tca_ld32(o_b + c, ow);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (row_ok) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
+                    for (int i = 0; i < 32; i += 8) {
                         uint4 o4;
-                        uint32_t* ow = reinterpret_cast<uint32_t*>(&o4);
+                        uint32_t* o32 = reinterpret_cast<uint32_t*>(&o4);
 #pragma unroll
                         for (int e = 0; e < 8; e += 2) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(ov[j + e]) * inv, __uint_as_float(ov[j + e + 1]) * inv);
-                            ow[e / 2] = *reinterpret_cast<uint32_t*>(&h2);
+                            float y0 = __uint_as_float(ov[i + e]) * wa, y1 = __uint_as_float(ov[i + e + 1]) * wa;
+                            if (two) {
+                                y0 += __uint_as_float(ow[i + e]) * wb;
+                                y1 += __uint_as_float(ow[i + e + 1]) * wb;
+                            }
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(y0, y1);
+                            o32[e / 2] = *reinterpret_cast<uint32_t*>(&h2);
                         }
-                        *reinterpret_cast<uint4*>(dst + c + j) = o4;
+                        *reinterpret_cast<uint4*>(dst + c + i) = o4;
                     }
                 }
             }
@@ -407,7 +534,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512));
     }
 }
 
@@ -429,12 +556,23 @@ static TcaEncodeFn tca_encode_fn() {
 
 // Tensor map over the cache pages of one layer ([rows, hd] bfloat16, rows = pages * kv_heads * page_size)
 // read in boxes of [page_size rows, 64 dims] with the 128-byte swizzle: the operand layout of tcgen05.mma.
-PICO_API int pico_make_kv_tensor_map_2d(void* map_out, const void* base, long long rows, int hd, int page_size) {
+// With `all_blocks` (the values) a box holds all 64-dim blocks of the page rows, one block after the other.
+PICO_API int pico_make_kv_tensor_map_2d(void* map_out, const void* base, long long rows, int hd, int page_size, int all_blocks) {
     if (hd % 64 != 0 || hd < 64 || hd > 128 || page_size < 8 || page_size > TCA_BN || TCA_BN % page_size != 0 ||
         (page_size & 7) != 0 || ((uintptr_t)base & 15) != 0)
         return PICO_ERR_SIZE;
     TcaEncodeFn fn = tca_encode_fn();
     if (!fn) return -7;
+    if (all_blocks) {
+        const cuuint64_t dims3[3] = {64, (cuuint64_t)rows, (cuuint64_t)(hd / 64)};
+        const cuuint64_t strides3[2] = {(cuuint64_t)hd * 2, 128};
+        const cuuint32_t box3[3] = {64, (cuuint32_t)page_size, (cuuint32_t)(hd / 64)};
+        const cuuint32_t estr3[3] = {1, 1, 1};
+        const CUresult r3 = fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims3,
+                               strides3, box3, estr3, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        return r3 == CUDA_SUCCESS ? 0 : -7;
+    }
     const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
     const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
@@ -459,8 +597,8 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
     const int tpt = TCA_BM / g;
     const dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_segs);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)(hd / 64 + 1) * TCA_BM * 128 + (size_t)TCA_STAGES * 2 * TCA_BN * hd * 2 +
-                        (2 * TCA_STAGES + 4) * 8 + 16 + TCA_TABLE_CACHE * 4 + 1024;
+    const size_t smem = (size_t)(hd / 64) * TCA_BM * 128 + (size_t)TCA_STAGES * 2 * TCA_BN * hd * 2 +
+                        (4 * TCA_STAGES + 8) * 8 + 16 + 2 * TCA_BM * 8 + TCA_TABLE_CACHE * 4 + 1024;
     CUtensorMap km, vm;
     memcpy(&km, k_map, sizeof(CUtensorMap));
     memcpy(&vm, v_map, sizeof(CUtensorMap));

@@ -66,7 +66,7 @@ def library():
                                   f32, i32, vp],
         "pico_paged_prefill_tma": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
         "pico_tma_status": [vp],
-        "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32],
+        "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32, i32],
         "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
         "pico_tca_status": [vp],
         "pico_gemm_tcgen05": [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp],
@@ -276,9 +276,10 @@ def make_kv_tensor_map(pages: torch.Tensor):
     return (buf, aligned)
 
 
-def make_kv_tensor_map_2d(pages: torch.Tensor):
+def make_kv_tensor_map_2d(pages: torch.Tensor, values: bool = False):
     """Like :func:`make_kv_tensor_map`, with boxes of [page_size rows, 64 dims]: the operand layout of
-    the tcgen05 prefill attention kernel.  None when the sizes are not taken."""
+    the tcgen05 prefill attention kernel; for the ``values`` a box holds all 64-dim blocks of the
+    page rows, one after the other.  None when the sizes are not taken."""
     if not pages.is_cuda or pages.dtype != torch.bfloat16 or not pages.is_contiguous() or pages.dim() != 4:
         return None
     n_pages, nkv, ps, hd = pages.shape
@@ -286,7 +287,7 @@ def make_kv_tensor_map_2d(pages: torch.Tensor):
         return None
     buf = (ctypes.c_ubyte * 192)()
     aligned = (ctypes.addressof(buf) + 63) & ~63
-    if library().pico_make_kv_tensor_map_2d(aligned, pages.data_ptr(), n_pages * nkv * ps, hd, ps) != 0:
+    if library().pico_make_kv_tensor_map_2d(aligned, pages.data_ptr(), n_pages * nkv * ps, hd, ps, 1 if values else 0) != 0:
         return None
     return (buf, aligned)
 

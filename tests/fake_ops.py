@@ -164,7 +164,7 @@ def make_kv_tensor_map(pages):
     return None
 
 
-def make_kv_tensor_map_2d(pages):
+def make_kv_tensor_map_2d(pages, values=False):
     return None
 
 

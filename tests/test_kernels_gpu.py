@@ -153,7 +153,7 @@ def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, se
         if tma:
             assert maps[0] is not None and maps[1] is not None
         if tc:
-            maps = maps + (ops.make_kv_tensor_map_2d(kd), ops.make_kv_tensor_map_2d(vd))
+            maps = maps + (ops.make_kv_tensor_map_2d(kd), ops.make_kv_tensor_map_2d(vd, values=True))
             assert maps[2] is not None and maps[3] is not None
         ops.paged_attention_mma(q.to(DEV), kd, vd, out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
                                 cu.to(DEV), pf.to(DEV), len(pf), max([n for n in q_lens if n > 1], default=0),
