@@ -41,6 +41,7 @@
 #ifndef SG_ST_DEEP
 #define SG_ST_DEEP 8          // ... when there are fewer tiles than SMs (one block per SM)
 #endif
+#define SG_NORM_CACHE 12       // float4 per lane of a row kept in registers by the norm prologue (rows up to 1536 wide)
 #ifndef SG_CTAS_PER_SM
 #define SG_CTAS_PER_SM 2
 #endif
@@ -219,22 +220,26 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
     const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int total = my_tiles * nkw;                            // this warp's pipeline steps
 
-    auto load_step = [&](int it) {
+    // one pipeline step of this warp: 16 weight rows x 64 k (and, when they are streamed, the
+    // activations of the same k) into the step's stage
+    auto load_step = [&](int it, bool weights, bool acts) {
         const int li = it / nkw, j = it - li * nkw;
-        int ra, rb;
-        sg_rows<EPI>(p, blockIdx.x + li * gridDim.x, ra, rb);
         bf16* ws = ring + (it % STAGES) * STAGE_ELEMS;
         const int k0 = (warp + SG_WARPS * j) * SG_KW;
+        if (weights) {
+            int ra, rb;
+            sg_rows<EPI>(p, blockIdx.x + li * gridDim.x, ra, rb);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {                            // 16 rows x 8 chunks of 16 bytes
-            const int idx = lane + 32 * q;
-            const int r = idx >> 3, c = idx & 7;
-            const int k = k0 + c * 8;
-            const int row = (r < 8 ? ra + r : rb + r - 8);
-            const bool ok = k < p.K;
-            sg_cp16(sg_smem_u32(ws + r * SG_LD + c * 8), p.w + (size_t)row * p.K + (ok ? k : 0), ok);
+            for (int q = 0; q < 4; ++q) {                        // 16 rows x 8 chunks of 16 bytes
+                const int idx = lane + 32 * q;
+                const int r = idx >> 3, c = idx & 7;
+                const int k = k0 + c * 8;
+                const int row = (r < 8 ? ra + r : rb + r - 8);
+                const bool ok = k < p.K;
+                sg_cp16(sg_smem_u32(ws + r * SG_LD + c * 8), p.w + (size_t)row * p.K + (ok ? k : 0), ok);
+            }
         }
-        if (!XPRE) {
+        if (!XPRE && acts) {
             bf16* xs = ws + 16 * SG_LD;
 #pragma unroll
             for (int q = 0; q < MT * 2; ++q) {                   // XR rows x 8 chunks
@@ -252,8 +257,19 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
         // and only then does the block wait for that kernel's output, the activations
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (s < total) load_step(s);
+            if (s < total) load_step(s, true, false);
             sg_commit();
+        }
+        // the norm weights do not depend on the kernel before either: a lane's share of them (K up to
+        // SG_NORM_CACHE * 128) is in registers before the wait
+        float4 nw[SG_NORM_CACHE];
+        const bool cached = p.xf != nullptr && p.K <= SG_NORM_CACHE * 128 && p.K % 4 == 0;
+        if (cached) {
+#pragma unroll
+            for (int i = 0; i < SG_NORM_CACHE; ++i) {
+                const int k = lane * 4 + i * 128;
+                nw[i] = k < p.K ? *reinterpret_cast<const float4*>(p.norm_w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
         pdl_wait();
         if (p.xf) {
@@ -267,6 +283,33 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
                     continue;
                 }
                 const float* src = p.xf + (size_t)(p.x_rows ? p.x_rows[r] : r) * p.K;
+                if (cached) {
+                    // one pass: the row is read once into registers, summed, scaled and stored
+                    float4 xv[SG_NORM_CACHE];
+                    float ss = 0.f;
+#pragma unroll
+                    for (int i = 0; i < SG_NORM_CACHE; ++i) {
+                        const int k = lane * 4 + i * 128;
+                        xv[i] = k < p.K ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int i = 0; i < SG_NORM_CACHE; ++i) ss += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
+                    ss = warp_sum(ss);
+                    const float inv = 1.0f / sqrtf(ss / (float)p.K + p.eps);
+#pragma unroll
+                    for (int i = 0; i < SG_NORM_CACHE; ++i) {
+                        const int k = lane * 4 + i * 128;
+                        if (k < kpad) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(xv[i].x * inv * nw[i].x, xv[i].y * inv * nw[i].y);
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(xv[i].z * inv * nw[i].z, xv[i].w * inv * nw[i].w);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(dst + k) = pk;
+                        }
+                    }
+                    continue;
+                }
                 float ss = 0.f;
                 for (int k = lane * 4; k < p.K; k += 128) {
                     const float4 v = *reinterpret_cast<const float4*>(src + k);
@@ -301,10 +344,15 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
         sg_wait<0>();            // once per block: the activations (and the first weight stages) have landed
         __syncthreads();
     } else {
+        // the same here: the weights of the first stages are asked for before the wait, the
+        // activations that go with them after it
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s)
+            if (s < total) load_step(s, true, false);
         pdl_wait();
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (s < total) load_step(s);
+            if (s < total) load_step(s, false, true);
             sg_commit();
         }
     }
@@ -319,7 +367,7 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
         for (int j = 0; j < nkw; ++j, ++it) {
             sg_wait<STAGES - 2>();
             __syncwarp();
-            if (it + STAGES - 1 < total) load_step(it + STAGES - 1);
+            if (it + STAGES - 1 < total) load_step(it + STAGES - 1, true, true);
             sg_commit();
             const bf16* ws = ring + (it % STAGES) * STAGE_ELEMS;
             const bf16* xs = XPRE ? x_all + (warp + SG_WARPS * j) * SG_KW : ws + 16 * SG_LD;
