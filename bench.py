@@ -314,12 +314,14 @@ def run_micro(args):
             w = (torch.randn(N, K, device=dev) / math.sqrt(K)).bfloat16()
             fl = 2.0 * M * N * K
             if name == "gate_up":
-                t = graph_time([lambda: ops.tc_gate_up_swiglu(x, w)] * 8)
+                t1 = graph_time([lambda: ops.tc_gate_up_swiglu(x, w, pair=False)] * 8)
+                t = graph_time([lambda: ops.tc_gate_up_swiglu(x, w, pair=True)] * 8)
             else:
-                t = graph_time([lambda: ops.tc_linear(x, w)] * 8)
+                t1 = graph_time([lambda: ops.tc_linear(x, w, pair=False)] * 8)
+                t = graph_time([lambda: ops.tc_linear(x, w, pair=True)] * 8)
             tc = graph_time([lambda: torch.mm(x, w.t())] * 8)
-            out[f"tcgen05_{name}"] = {"us": round(t, 1), "tflops": round(fl / t / 1e6), "cublas_us": round(tc, 1),
-                                      "fused": "swiglu" if name == "gate_up" else None}
+            out[f"tcgen05_{name}"] = {"us": round(t, 1), "tflops": round(fl / t / 1e6), "one_sm_us": round(t1, 1),
+                                      "cublas_us": round(tc, 1), "fused": "swiglu" if name == "gate_up" else None}
         # causal attention of one prompt of M tokens over its own pages
         nh, nkv, hd, ps = 12, 2, 128, 16
         blocks = (M + ps - 1) // ps

@@ -67,6 +67,96 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const fl
     }
 }
 
+// The same for bfloat16 with 16-byte accesses: a thread takes 8 consecutive pairs (dims i..i+7 and
+// i + hd/2 .. of one head) or 8 consecutive dims of a value head; a block takes ROPE_TPB tokens.
+// Needs hd % 16 == 0, rot_half % 8 == 0, row_stride % 8 == 0 and 16-byte aligned buffers.
+#define ROPE_TPB 4
+__device__ __forceinline__ void rope_unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 p = __bfloat1622float2(h[i]);
+        f[2 * i] = p.x;
+        f[2 * i + 1] = p.y;
+    }
+}
+__device__ __forceinline__ uint4 rope_pack8(const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+__device__ __forceinline__ void rope_add_bias8(const float* __restrict__ b, float (&f)[8]) {
+    const float4 b0 = *reinterpret_cast<const float4*>(b), b1 = *reinterpret_cast<const float4*>(b + 4);
+    f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+    f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+}
+
+__global__ void __launch_bounds__(256)
+rope_store_bf16x8_kernel(bf16* __restrict__ qkv, int row_stride, const float* __restrict__ bias,
+                         const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                         const int* __restrict__ slots, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int T,
+                         int nh, int nkv, int hd, int rot_half, int page_size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float cs[];  // [ROPE_TPB][cos[rot_half], sin[rot_half]]
+    const int t0 = blockIdx.x * ROPE_TPB;
+    for (int idx = threadIdx.x; idx < ROPE_TPB * rot_half; idx += blockDim.x) {
+        const int tt = idx / rot_half, i = idx - tt * rot_half;
+        if (t0 + tt < T) {
+            float s, c;
+            sincosf((float)positions[t0 + tt] * inv_freq[i], &s, &c);
+            cs[tt * 2 * rot_half + i] = c;
+            cs[tt * 2 * rot_half + rot_half + i] = s;
+        }
+    }
+    __syncthreads();
+    const int half = hd / 2, gph = half / 8;               // groups of 8 pairs per head
+    const int rot_items = (nh + nkv) * gph, v_items = nkv * (hd / 8), items = rot_items + v_items;
+    for (int idx = threadIdx.x; idx < ROPE_TPB * items; idx += blockDim.x) {
+        const int tt = idx / items, w = idx - tt * items;
+        const int t = t0 + tt;
+        if (t >= T) break;
+        bf16* row = qkv + (size_t)t * row_stride;
+        const int slot = slots ? slots[t] : -1;
+        const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+        if (w < rot_items) {
+            const int head = w / gph, i = (w - head * gph) * 8;
+            if (head >= nh && slot < 0) continue;            // keys of a token that is not stored
+            const int c0 = head * hd + i, c1 = c0 + half;
+            float x1[8], x2[8];
+            rope_unpack8(*reinterpret_cast<const uint4*>(row + c0), x1);
+            rope_unpack8(*reinterpret_cast<const uint4*>(row + c1), x2);
+            if (bias) {
+                rope_add_bias8(bias + c0, x1);
+                rope_add_bias8(bias + c1, x2);
+            }
+            if (i < rot_half) {
+                const float* cp = cs + tt * 2 * rot_half + i;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float c = cp[e], sn = cp[rot_half + e];
+                    const float y1 = x1[e] * c - x2[e] * sn, y2 = x2[e] * c + x1[e] * sn;
+                    x1[e] = y1;
+                    x2[e] = y2;
+                }
+            }
+            bf16* dst = head < nh ? row + c0 : k_pages + (((size_t)page * nkv + (head - nh)) * page_size + off) * hd + i;
+            *reinterpret_cast<uint4*>(dst) = rope_pack8(x1);
+            *reinterpret_cast<uint4*>(dst + half) = rope_pack8(x2);
+        } else if (slot >= 0) {
+            const int j = (w - rot_items) * 8;               // 8 dims of the value part
+            const int kh = j / hd, d = j - kh * hd;
+            const int c = (nh + nkv) * hd + j;
+            float v[8];
+            rope_unpack8(*reinterpret_cast<const uint4*>(row + c), v);
+            if (bias) rope_add_bias8(bias + c, v);
+            *reinterpret_cast<uint4*>(v_pages + (((size_t)page * nkv + kh) * page_size + off) * hd + d) = rope_pack8(v);
+        }
+    }
+}
+
 // qkv: [T, row_stride] with columns q heads, k heads, v heads.  slots may be null (a layer that
 // reads another layer's cache rotates its queries only); a slot of -1 skips that token's store.
 PICO_API int pico_rope_store(void* qkv, int row_stride, const float* bias, const int* positions,
@@ -80,7 +170,15 @@ PICO_API int pico_rope_store(void* qkv, int row_stride, const float* bias, const
     if (smem > 48 * 1024) return PICO_ERR_SIZE;
     const int work = (nh + nkv) * (hd / 2);
     const int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
-    if (act_dtype == PICO_F32)
+    const bool vec = act_dtype == PICO_BF16 && hd % 16 == 0 && rot_half % 8 == 0 && row_stride % 8 == 0 &&
+                     ((uintptr_t)qkv & 15) == 0 && (!bias || ((uintptr_t)bias & 15) == 0) &&
+                     (!slots || (((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0)) &&
+                     (size_t)ROPE_TPB * smem <= 48 * 1024;
+    if (vec)
+        pico_launch(rope_store_bf16x8_kernel, dim3((T + ROPE_TPB - 1) / ROPE_TPB), dim3(256), (size_t)ROPE_TPB * smem, stream,
+                    (bf16*)qkv, row_stride, bias, positions, inv_freq, slots, (bf16*)k_pages, (bf16*)v_pages, T, nh, nkv, hd,
+                    rot_half, page_size);
+    else if (act_dtype == PICO_F32)
         pico_launch((rope_store_kernel<float>), dim3(T), dim3(threads), smem, stream, (float*)qkv, row_stride, bias, positions, inv_freq,
                                                                slots, (float*)k_pages, (float*)v_pages, nh, nkv, hd,
                                                                rot_half, page_size);

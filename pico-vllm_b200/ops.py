@@ -71,6 +71,8 @@ def library():
         "pico_tca_status": [vp],
         "pico_gemm_tcgen05": [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp],
         "pico_tc_status": [vp],
+        "pico_gemm_tcgen05_pair": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
+        "pico_tp_status": [vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
         "pico_bf16_to_f32": [vp, vp, i64, vp],
     }
@@ -524,13 +526,33 @@ def tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def tc_status() -> int:
-    """0, or 1 when a tcgen05 kernel gave up waiting on a barrier since the library was loaded."""
-    out = ctypes.c_int(0)
+    """0, or 1 when a tcgen05 product kernel gave up waiting on a barrier since the library was loaded."""
+    out, out2 = ctypes.c_int(0), ctypes.c_int(0)
     library().pico_tc_status(ctypes.addressof(out))
-    return out.value
+    library().pico_tp_status(ctypes.addressof(out2))
+    return out.value | out2.value
 
 
-def tc_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+TC_PAIR_MIN_TOKENS = 256      # from here on two SMs share a tile (tcgen05.mma.cta_group::2)
+
+
+def _tc_gemm(x, weight, out, residual, M, N, K, epi, pair, what):
+    """One of the two tcgen05 product kernels: a tile per block, or per pair of blocks (``pair``:
+    None = by the number of tokens, True = the pair form with the tile it picks, 256 or 512 = the
+    pair form with that many rows of x per pair)."""
+    if pair is None:
+        pair = M >= TC_PAIR_MIN_TOKENS
+    if pair:
+        rows = 0 if pair is True else int(pair)
+        _check(library().pico_gemm_tcgen05_pair(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), _ptr(residual), M, N, K,
+                                                epi, rows, _stream()), "gemm_tcgen05_pair" + what)
+    else:
+        _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), _ptr(residual), M, N, K, epi,
+                                           _stream()), "gemm_tcgen05" + what)
+    _count()
+
+
+def tc_linear(x: torch.Tensor, weight: torch.Tensor, pair=None) -> torch.Tensor:
     """x [M, K] times weight[N, K] transposed on the tcgen05 tensor cores; bfloat16 out."""
     _cuda(x, weight)
     if not tc_takes(x, weight):
@@ -538,13 +560,12 @@ def tc_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     M, K = x.shape
     N = weight.shape[0]
     out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-    _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), None, M, N, K, 0, _stream()),
-           "gemm_tcgen05")
-    _count()
+    _tc_gemm(x, weight, out, None, M, N, K, 0, pair, "")
     return out
 
 
-def tc_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> None:
+def tc_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
+                       pair=None) -> None:
     """residual [M, N] float32 += x [M, K] times weight[N, K] transposed."""
     _cuda(x, weight, residual)
     M, K = x.shape
@@ -552,12 +573,10 @@ def tc_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Te
     if not tc_takes(x, weight) or residual.dtype != torch.float32 or residual.shape != (M, N) \
             or not residual.is_contiguous():
         raise KernelError("tc_linear_residual: sizes not taken")
-    _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(weight), None, _ptr(residual), M, N, K, 1,
-                                       _stream()), "gemm_tcgen05 (residual)")
-    _count()
+    _tc_gemm(x, weight, None, residual, M, N, K, 1, pair, " (residual)")
 
 
-def tc_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+def tc_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor, pair=None) -> torch.Tensor:
     """silu(x wg^T) * (x wu^T) for gate_up_weight = [wg; wu]; returns [M, I] bfloat16."""
     _cuda(x, gate_up_weight)
     if not tc_takes(x, gate_up_weight):
@@ -565,9 +584,7 @@ def tc_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Te
     M, K = x.shape
     I = gate_up_weight.shape[0] // 2
     out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
-    _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(gate_up_weight), _ptr(out), None, M, 2 * I, K, 2,
-                                       _stream()), "gemm_tcgen05 (swiglu)")
-    _count()
+    _tc_gemm(x, gate_up_weight, out, None, M, 2 * I, K, 2, pair, " (swiglu)")
     return out
 
 

@@ -387,30 +387,32 @@ def test_skinny_kernels_with_the_norm_inside(M, K, eps):
     assert torch.allclose(kg.cpu().float(), kr.float(), **t) and torch.allclose(vg.cpu().float(), vr.float(), **t)
 
 
+@pytest.mark.parametrize("pair", [False, True, 512])
 @pytest.mark.parametrize("M", [128, 200, 2048, 777])
 @pytest.mark.parametrize("N,K", [(256, 64), (2048, 1536), (1536, 1536), (1536, 8960), (272, 200), (512, 192)])
-def test_tcgen05_linear_store_and_residual(M, N, K):
+def test_tcgen05_linear_store_and_residual(M, N, K, pair):
     from pico_vllm_b200 import ops
     x = torch.randn(M, K, generator=gen(90)).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=gen(91)) / math.sqrt(K)).to(torch.bfloat16)
     want = x.float() @ w.float().t()
-    got = ops.tc_linear(x.to(DEV), w.to(DEV)).cpu().float()
+    got = ops.tc_linear(x.to(DEV), w.to(DEV), pair=pair).cpu().float()
     assert torch.allclose(got, want, atol=3e-2, rtol=2e-2)
     res = torch.randn(M, N, generator=gen(92))
     rg = res.to(DEV)
-    ops.tc_linear_residual(x.to(DEV), w.to(DEV), rg)
+    ops.tc_linear_residual(x.to(DEV), w.to(DEV), rg, pair=pair)
     assert torch.allclose(rg.cpu(), res + want, atol=5e-3, rtol=5e-3)
     torch.cuda.synchronize()
     assert ops.tc_status() == 0
 
 
+@pytest.mark.parametrize("pair", [False, True, 512])
 @pytest.mark.parametrize("M", [128, 333, 2048])
 @pytest.mark.parametrize("I,K", [(128, 64), (8960, 1536), (320, 192), (176, 80)])
-def test_tcgen05_gate_up_swiglu(M, I, K):
+def test_tcgen05_gate_up_swiglu(M, I, K, pair):
     from pico_vllm_b200 import ops
     x = torch.randn(M, K, generator=gen(93)).to(torch.bfloat16)
     w = (torch.randn(2 * I, K, generator=gen(94)) * 2 / math.sqrt(K)).to(torch.bfloat16)
-    got = ops.tc_gate_up_swiglu(x.to(DEV), w.to(DEV)).cpu().float()
+    got = ops.tc_gate_up_swiglu(x.to(DEV), w.to(DEV), pair=pair).cpu().float()
     want = fake_ops.skinny_gate_up_swiglu(x, w).float()
     assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
     torch.cuda.synchronize()
