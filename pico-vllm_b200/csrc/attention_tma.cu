@@ -105,7 +105,7 @@ __device__ __forceinline__ uint32_t swz_addr(uint32_t tile, int key, int dim) {
 // CW consumer warps in groups of four: group i takes tiles i, i + CW/4, ... (a group multiplies one tile,
 // 16 cache positions per warp).  One group is latency-bound at about 0.8 us per tile, so with one
 // block per SM two groups are used; with two blocks per SM one group each.
-template <int HD, int TMA_STAGES, int CW>     // head size 64 or 128; stages; consumer warps (4 or 8)
+template <int HD, int TMA_STAGES, int CW, int NT>     // head size 64 or 128; stages; consumer warps (4 or 8); 8-head tiles (g <= 8 NT)
 __global__ void __launch_bounds__((CW + 1) * 32)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
@@ -219,17 +219,29 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     cp_async_wait<0>();
     consumer_sync<CW * 32>();                                             // the queries are in shared memory
 
-    float o[HD / 8][4];
+    // The products are taken the other way round than in a prompt kernel: the 16 cache positions of a
+    // warp are the 16 ROWS of the tensor-core tile and the query heads its 8 columns, because a token
+    // brings at most 16 heads (NT tiles of 8) and a tile of 8 columns costs half the instructions of two:
+    //   S^T [16 keys x 8 heads] = K [16 keys x hd] Q^T;   O^T [hd x 8 heads] += V^T [hd x 16 keys] P^T.
+    // A thread then holds, of S^T and P^T, keys lane/4 and lane/4 + 8 and heads 2 (lane%4), + 1; the
+    // maxima and sums of a head run over the 8 lanes with the same lane%4.
+    float o[NT][HD / 16][4];
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
-    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
-    const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < HD / 16; ++i) o[nt][i][0] = o[nt][i][1] = o[nt][i][2] = o[nt][i][3] = 0.f;
+    float m[NT][2], l[NT][2];          // per head column of the thread: running maximum (all keys so far, log2 units), this thread's part of the sum
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) m[nt][0] = m[nt][1] = -INFINITY, l[nt][0] = l[nt][1] = 0.f;
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;       // K as the 16-row operand
+    const int b_row = lane & 7, b_col = ((lane >> 3) & 1) * 8;                           // Q rows as the 8-column operand
+    const int v_row = (lane & 7) + (lane >> 4) * 8, v_col = ((lane >> 3) & 1) * 8;       // V^T through the transposing load
     // the queries are the same for every tile: their fragments stay in registers
-    uint32_t qf[HD / 16][4];
+    uint32_t qf[NT][HD / 16][2];
 #pragma unroll
-    for (int k0 = 0; k0 < HD; k0 += 16) ldmatrix_x4(qf[k0 / 16], smem_u32(q_s + a_row * QLD + k0 + a_col));
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int k0 = 0; k0 < HD; k0 += 16) ldmatrix_x2(qf[nt][k0 / 16], smem_u32(q_s + (nt * 8 + b_row) * QLD + k0 + b_col));
 
     for (int it = grp; it < ntiles; it += NG) {
         const int s = it % TMA_STAGES;
@@ -244,65 +256,92 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         const int kw = wq * 16;                                  // this warp's 16 positions of the tile
         const int w0 = n0 + kw;
         if (w0 < hi && w0 + 16 > lo) {
-            // q.k over the head dimension in two independent chains (even and odd steps of 16), so
-            // that one tensor-core instruction does not wait for the one before it
-            float sc[2][4], sc2[2][4];
+            // q.k: four independent accumulators per head tile (a tensor-core instruction waits more
+            // than a hundred clocks for the one before it when both add into the same registers)
+            float sc[NT][4][4];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
-                sc2[j][0] = sc2[j][1] = sc2[j][2] = sc2[j][3] = 0.f;
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sc[nt][c][0] = sc[nt][c][1] = sc[nt][c][2] = sc[nt][c][3] = 0.f;
+#pragma unroll
+            for (int k0 = 0; k0 < HD; k0 += 16) {
+                uint32_t a[4];
+                ldmatrix_x4(a, swz_addr<HD>(kt, kw + a_row, k0 + a_col));
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_bf16(sc[nt][(k0 / 16) & 3], a, qf[nt][k0 / 16][0], qf[nt][k0 / 16][1]);
             }
+            const int key_a = w0 + (lane >> 2), key_b = key_a + 8;                   // the thread's two cache positions
+            const bool vis_a = key_a >= lo && key_a < hi, vis_b = key_b >= lo && key_b < hi;
+            const bool warp_edge = __any_sync(0xffffffffu, !(vis_a && vis_b));
+            uint32_t pb[NT][2];                                  // P^T as the 8-column operand: keys 0-7 and 8-15 of the warp
 #pragma unroll
-            for (int k0 = 0; k0 < HD; k0 += 32) {
-                uint32_t b[4], b2[4];
-                ldmatrix_x4(b, swz_addr<HD>(kt, kw + b_row, k0 + b_col));
-                ldmatrix_x4(b2, swz_addr<HD>(kt, kw + b_row, k0 + 16 + b_col));
-                mma_bf16(sc[0], qf[k0 / 16], b[0], b[1]);
-                mma_bf16(sc[1], qf[k0 / 16], b[2], b[3]);
-                mma_bf16(sc2[0], qf[k0 / 16 + 1], b2[0], b2[1]);
-                mma_bf16(sc2[1], qf[k0 / 16 + 1], b2[2], b2[3]);
-            }
-            bool edge = false;                                   // some of the 16 positions are not visible
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
+            for (int nt = 0; nt < NT; ++nt) {
+                float x[4];                                      // [key a: head 0, 1; key b: head 0, 1]
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int n = w0 + j * 8 + (lane & 3) * 2 + (e & 1);
-                    const bool vis = n >= lo && n < hi;
-                    edge |= !vis;
-                    sc[j][e] = vis ? (sc[j][e] + sc2[j][e]) * scale_log2 : -INFINITY;
+                    const float v = (sc[nt][0][e] + sc[nt][1][e]) + (sc[nt][2][e] + sc[nt][3][e]);
+                    x[e] = ((e < 2) ? vis_a : vis_b) ? v * scale_log2 : -INFINITY;
                 }
-            online_softmax<HD, 2>(sc, m, l, o);
-            // p.v: invisible positions have p = 0 exactly, but their value rows may hold anything
-            // (another request's data, or not-a-number): they are read as zero
-            const bool warp_edge = __any_sync(0xffffffffu, edge);
-            uint32_t a[4];
-            a[0] = pack_bf16(sc[0][0], sc[0][1]);
-            a[1] = pack_bf16(sc[0][2], sc[0][3]);
-            a[2] = pack_bf16(sc[1][0], sc[1][1]);
-            a[3] = pack_bf16(sc[1][2], sc[1][3]);
-            const int vkey = kw + v_row;
+                float p[4];
 #pragma unroll
-            for (int d0 = 0; d0 < HD; d0 += 16) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, swz_addr<HD>(vt, vkey, d0 + v_col));
-                if (warp_edge) {
-                    // after the transposing load, register j of lane L holds the values of cache
-                    // positions w0 + (j&1)*8 + (L%4)*2 + {0, 1} (low and high half): clear by position
+                for (int h = 0; h < 2; ++h) {
+                    float mx = fmaxf(x[h], x[2 + h]);
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    const float m_new = fmaxf(m[nt][h], mx);
+                    const float corr = m_new == -INFINITY ? 1.f : fast_exp2(m[nt][h] - m_new);
+                    const float sub = m_new == -INFINITY ? 0.f : m_new;
+                    p[h] = fast_exp2(x[h] - sub);
+                    p[2 + h] = fast_exp2(x[2 + h] - sub);
+                    l[nt][h] = l[nt][h] * corr + p[h] + p[2 + h];
+                    m[nt][h] = m_new;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int key0 = n0 + kw + (j & 1) * 8 + (lane & 3) * 2;
-                        const bool ok0 = key0 >= lo && key0 < hi, ok1 = key0 + 1 >= lo && key0 + 1 < hi;
-                        b[j] &= (ok0 ? 0x0000ffffu : 0u) | (ok1 ? 0xffff0000u : 0u);
+                    for (int i = 0; i < HD / 16; ++i) {
+                        o[nt][i][h] *= corr;
+                        o[nt][i][2 + h] *= corr;
                     }
                 }
-                mma_bf16(o[d0 / 8], a, b[0], b[1]);
-                mma_bf16(o[d0 / 8 + 1], a, b[2], b[3]);
+                // [key][head pair] -> [head][key pair]: the 8 x 8 transpose between the layout a product
+                // leaves and the layout the next one reads as its 8-column operand
+                const uint32_t pa = pack_bf16(p[0], p[1]), pc = pack_bf16(p[2], p[3]);
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(pb[nt][0]) : "r"(pa));
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(pb[nt][1]) : "r"(pc));
+            }
+            // p.v: invisible positions have p = 0 exactly, but their value rows may hold anything
+            // (another request's data, or not-a-number): they are read as zero
+#pragma unroll
+            for (int d0 = 0; d0 < HD; d0 += 16) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, swz_addr<HD>(vt, kw + v_row, d0 + v_col));
+                if (warp_edge) {
+                    // register j of lane L holds dims d0 + L/4 (+ 8 for odd j) of cache positions
+                    // w0 + (j / 2) * 8 + (L % 4) * 2 + {0, 1} (low and high half): clear by position
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int key0 = w0 + (j >> 1) * 8 + (lane & 3) * 2;
+                        const bool ok0 = key0 >= lo && key0 < hi, ok1 = key0 + 1 >= lo && key0 + 1 < hi;
+                        a[j] &= (ok0 ? 0x0000ffffu : 0u) | (ok1 ? 0xffff0000u : 0u);
+                    }
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][d0 / 16], a, pb[nt][0], pb[nt][1]);
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);                   // this warp is done with the stage
     }
+    // the sums of a head: over the 8 lanes that hold its keys
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float v = l[nt][h];
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            l[nt][h] = v;
+        }
     consumer_sync<CW * 32>();
     const bool dead = *abort_s != 0;
     if (dead && !cluster_reduce) return;
@@ -312,19 +351,21 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     float* fin_o = mml + CW * 16 * 2;                           // [16][HD]: this block's result, not normalised
     float* fin_ml = fin_o + 16 * HD;                            // [16][2]: its max (log2 units) and sum
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = (lane >> 2) + r * 8;
-        if ((lane & 3) == 0) {
-            mml[(warp * 16 + row) * 2] = m[r];
-            mml[(warp * 16 + row) * 2 + 1] = l[r];
-        }
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-            const int d = i * 8 + (lane & 3) * 2;
-            mo[(warp * 16 + row) * HD + d] = o[i][2 * r];
-            mo[(warp * 16 + row) * HD + d + 1] = o[i][2 * r + 1];
+        for (int h = 0; h < 2; ++h) {
+            const int row = nt * 8 + (lane & 3) * 2 + h;         // query head of the group
+            if ((lane >> 2) == 0) {
+                mml[(warp * 16 + row) * 2] = m[nt][h];
+                mml[(warp * 16 + row) * 2 + 1] = l[nt][h];
+            }
+#pragma unroll
+            for (int i = 0; i < HD / 16; ++i) {
+                const int d = i * 16 + (lane >> 2);
+                mo[(warp * 16 + row) * HD + d] = o[nt][i][h];
+                mo[(warp * 16 + row) * HD + d + 8] = o[nt][i][2 + h];
+            }
         }
-    }
     consumer_sync<CW * 32>();
     const float LN2 = 0.6931471805599453f;
     for (int idx = threadIdx.x; idx < g * HD; idx += CW * 32) {
@@ -640,14 +681,14 @@ int pico_launch_decode_combine(const float* part_o, const float* part_ml, void* 
                                int nh, int hd, int n_splits, cudaStream_t stream);
 
 // Can clusters of `size` blocks of the decode kernel run here?  (Asked once per configuration.)
-template <int HD, int ST, int CW>
+template <int HD, int ST, int CW, int NT>
 static bool tma_cluster_query(int size, size_t smem) {
-    if (size > 8 && cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+    if (size > 8 && cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW, NT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
                         cudaSuccess) {
         cudaGetLastError();
         return false;
     }
-    cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(size, 1, 1);
     cfg.blockDim = dim3((CW + 1) * 32);
@@ -660,21 +701,21 @@ static bool tma_cluster_query(int size, size_t smem) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, paged_decode_tma_kernel<HD, ST, CW>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, paged_decode_tma_kernel<HD, ST, CW, NT>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return false;
     }
     return n > 0;
 }
-static bool tma_cluster_ok(int hd, int size, bool few, size_t smem) {
-    static int cache[2][2][5];      // [hd 64/128][few][log2 size]: 0 unknown, 1 yes, 2 no
+static bool tma_cluster_ok(int hd, int size, int nt, size_t smem) {
+    static int cache[2][2][5];      // [hd 64/128][head tiles - 1][log2 size]: 0 unknown, 1 yes, 2 no
     int lg = 0;
     while ((1 << lg) < size) ++lg;
-    int& c = cache[hd == 128 ? 1 : 0][few ? 1 : 0][lg];
+    int& c = cache[hd == 128 ? 1 : 0][nt - 1][lg];
     if (c == 0) {
         bool ok;
-        if (hd == 128) ok = few ? tma_cluster_query<128, TMA_STAGES_FEW, 8>(size, smem) : tma_cluster_query<128, TMA_STAGES_MANY, 4>(size, smem);
-        else ok = few ? tma_cluster_query<64, TMA_STAGES_FEW, 8>(size, smem) : tma_cluster_query<64, TMA_STAGES_MANY, 4>(size, smem);
+        if (hd == 128) ok = nt == 1 ? tma_cluster_query<128, TMA_STAGES_MANY, 4, 1>(size, smem) : tma_cluster_query<128, TMA_STAGES_MANY, 4, 2>(size, smem);
+        else ok = nt == 1 ? tma_cluster_query<64, TMA_STAGES_MANY, 4, 1>(size, smem) : tma_cluster_query<64, TMA_STAGES_MANY, 4, 2>(size, smem);
         c = ok ? 1 : 2;
     }
     return c == 1;
@@ -705,9 +746,10 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
     if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
     const dim3 grid(n_splits, nkv, n_tok);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const bool few = false;      // one block per SM with more stages or more consumer warps was measured slower: it keeps
-                                 // the next kernel's blocks (which prefetch under programmatic launch) off the SM
-    const int stages = few ? TMA_STAGES_FEW : TMA_STAGES_MANY;
+    // (one block per SM with more stages or eight consumer warps was measured slower: it keeps the next
+    // kernel's blocks, which prefetch under programmatic launch, off the SM)
+    const int stages = TMA_STAGES_MANY;
+    const int nt = g <= 8 ? 1 : 2;                               // tiles of 8 query heads
     const size_t smem = (size_t)stages * 2 * MMA_BN * hd * 2 + (size_t)16 * (hd + 8) * 2 + 2 * stages * 8 + 8 +
                         TMA_TABLE_CACHE * 4 + 1024;
     CUtensorMap km, vm;
@@ -716,20 +758,21 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
     // 2, 4, 8 or 16 splits: the splits of one (token, kv head) run as one thread-block cluster and are
     // added through distributed shared memory; otherwise through scratch and the combine kernel
     int cluster = 0;
-    if (n_splits == 2 || n_splits == 4 || n_splits == 8 || n_splits == 16) cluster = tma_cluster_ok(hd, n_splits, few, smem) ? 1 : 0;
+    if (n_splits == 2 || n_splits == 4 || n_splits == 8 || n_splits == 16) cluster = tma_cluster_ok(hd, n_splits, nt, smem) ? 1 : 0;
     if (n_splits > 1 && !cluster && (!part_o || !part_ml)) return PICO_ERR_SIZE;
-#define LAUNCH_TMA(HD, ST, CW)                                                                                          \
+#define LAUNCH_TMA(HD, NT)                                                                                              \
     do {                                                                                                                \
-        cudaFuncSetAttribute(paged_decode_tma_kernel<HD, ST, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        pico_launch_cluster((paged_decode_tma_kernel<HD, ST, CW>), grid, dim3((CW + 1) * 32), smem, stream,             \
+        cudaFuncSetAttribute(paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                             (int)smem);                                                                                \
+        pico_launch_cluster((paged_decode_tma_kernel<HD, TMA_STAGES_MANY, 4, NT>), grid, dim3(5 * 32), smem, stream,    \
                             cluster ? n_splits : 1, km, vm, (const bf16*)q, q_row_stride, (bf16*)out, part_o,           \
                             part_ml, tok_list, tok_seg, positions, block_table, table_stride, nh, nkv, page_size,       \
                             window, scale_log2, n_splits, cluster);                                                     \
     } while (0)
     if (hd == 64) {
-        if (few) LAUNCH_TMA(64, TMA_STAGES_FEW, 8); else LAUNCH_TMA(64, TMA_STAGES_MANY, 4);
+        if (nt == 1) LAUNCH_TMA(64, 1); else LAUNCH_TMA(64, 2);
     } else {
-        if (few) LAUNCH_TMA(128, TMA_STAGES_FEW, 8); else LAUNCH_TMA(128, TMA_STAGES_MANY, 4);
+        if (nt == 1) LAUNCH_TMA(128, 1); else LAUNCH_TMA(128, 2);
     }
 #undef LAUNCH_TMA
     if (n_splits > 1 && !cluster)
