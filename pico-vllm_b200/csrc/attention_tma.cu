@@ -26,7 +26,7 @@
 #ifndef TMA_L2_PROMO
 #define TMA_L2_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
 #endif
-#define TMA_TABLE_CACHE 1024       // block-table entries of a block's key range kept in shared memory
+#define TMA_TABLE_CACHE 256        // block-table entries of a block's key range kept in shared memory
 
 __device__ int g_tma_status = 0;     // 0 = fine; 1 = a wait on a TMA copy ran out
 
@@ -83,6 +83,11 @@ __device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(raddr) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_cluster_f32(float* local, int rank, float v) {
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(raddr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(raddr), "f"(v) : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
 template <int NTHREADS> __device__ __forceinline__ void consumer_sync() {
@@ -126,7 +131,9 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     uint64_t* empty = full + TMA_STAGES;                                             // [stages]
     volatile int* abort_s = reinterpret_cast<volatile int*>(empty + TMA_STAGES);
     int* tbl_s = const_cast<int*>(abort_s) + 2;                                      // [TMA_TABLE_CACHE]
+    float* recv_o = reinterpret_cast<float*>(tbl_s + TMA_TABLE_CACHE);               // [splits][share]: what the cluster's blocks push here
     const int g = nh / nkv;
+    float* recv_ml = recv_o + n_splits * ((g * HD + n_splits - 1) / n_splits);       // [splits][16 rows][max, sum]
     const int kh = blockIdx.y, sp = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
@@ -199,10 +206,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
                             full + s);
             }
         }
-        if (cluster_reduce) {        // every thread of the cluster takes part in its two barriers
-            cluster_sync_all();
-            cluster_sync_all();
-        }
+        if (cluster_reduce) cluster_sync_all();     // every thread of the cluster takes part in its barrier
         return;
     }
     // -------------------------------------------------------------------- consumers (warps 0..CW-1)
@@ -346,10 +350,9 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     const bool dead = *abort_s != 0;
     if (dead && !cluster_reduce) return;
     // merge the four warps: (m, l, o) of each warp -> shared memory (all copies have landed and been used)
-    float* mo = reinterpret_cast<float*>(tiles);                // [CW warps][16 rows][HD]
-    float* mml = mo + CW * 16 * HD;                             // [CW][16][2]
-    float* fin_o = mml + CW * 16 * 2;                           // [16][HD]: this block's result, not normalised
-    float* fin_ml = fin_o + 16 * HD;                            // [16][2]: its max (log2 units) and sum
+    constexpr int MO_LD = HD + 4;                               // padded rows: the four head rows of a lane group fall into different banks
+    float* mo = reinterpret_cast<float*>(tiles);                // [CW warps][16 rows][MO_LD]
+    float* mml = mo + CW * 16 * MO_LD;                          // [CW][16][2]
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -362,13 +365,20 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
             for (int i = 0; i < HD / 16; ++i) {
                 const int d = i * 16 + (lane >> 2);
-                mo[(warp * 16 + row) * HD + d] = o[nt][i][h];
-                mo[(warp * 16 + row) * HD + d + 8] = o[nt][i][2 + h];
+                mo[(warp * 16 + row) * MO_LD + d] = o[nt][i][h];
+                mo[(warp * 16 + row) * MO_LD + d + 8] = o[nt][i][2 + h];
             }
         }
     consumer_sync<CW * 32>();
     const float LN2 = 0.6931471805599453f;
-    for (int idx = threadIdx.x; idx < g * HD; idx += CW * 32) {
+    // With a cluster, block sp adds output elements [sp * share, (sp + 1) * share) of the g * HD over all
+    // blocks: every block PUSHES what it has of another block's share (and its maxima and sums) into
+    // that block's receive area through distributed shared memory, one cluster barrier follows, and
+    // each block then adds from its own shared memory - nobody reads remote memory after the barrier,
+    // so blocks may leave at once.
+    const int total = g * HD;
+    const int share = (total + n_splits - 1) / n_splits;
+    for (int idx = threadIdx.x; idx < total; idx += CW * 32) {
         const int row = idx / HD, d = idx - row * HD;
         float M = -INFINITY;
 #pragma unroll
@@ -380,17 +390,20 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
             if (mw != -INFINITY) {
                 const float f = fast_exp2(mw - M);
                 L += mml[(w * 16 + row) * 2 + 1] * f;
-                acc += mo[(w * 16 + row) * HD + d] * f;
+                acc += mo[(w * 16 + row) * MO_LD + d] * f;
             }
         }
         const int h = kh * g + row;
         if (n_splits == 1) {
             out[((size_t)t * nh + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         } else if (cluster_reduce) {
-            fin_o[row * HD + d] = acc;
+            const int r = idx / share;
+            st_cluster_f32(recv_o + sp * share + (idx - r * share), r, acc);
             if (d == 0) {
-                fin_ml[row * 2] = M;
-                fin_ml[row * 2 + 1] = L;
+                for (int rr = 0; rr < n_splits; ++rr) {
+                    st_cluster_f32(recv_ml + (sp * 16 + row) * 2, rr, M);
+                    st_cluster_f32(recv_ml + (sp * 16 + row) * 2 + 1, rr, L);
+                }
             }
         } else {
             const size_t slot = ((size_t)t * nh + h) * n_splits + sp;
@@ -402,31 +415,25 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         }
     }
     if (!cluster_reduce || n_splits == 1) return;
-    // The splits of one (token, kv head) are the blocks of one cluster: each block adds, over all
-    // blocks, its share of the g * HD outputs, reading the others' results through distributed
-    // shared memory - no scratch in global memory, no second kernel.
     cluster_sync_all();
     {
-        const int total = g * HD;
-        const int share = (total + n_splits - 1) / n_splits;
         const int lo_i = sp * share, hi_i = min(total, lo_i + share);
         for (int idx = lo_i + (int)threadIdx.x; idx < hi_i; idx += CW * 32) {
             const int row = idx / HD, d = idx - row * HD;
             float M = -INFINITY;
-            for (int r = 0; r < n_splits; ++r) M = fmaxf(M, ld_cluster_f32(fin_ml + row * 2, r));
+            for (int r = 0; r < n_splits; ++r) M = fmaxf(M, recv_ml[(r * 16 + row) * 2]);
             float L = 0.f, acc = 0.f;
             for (int r = 0; r < n_splits; ++r) {
-                const float mr = ld_cluster_f32(fin_ml + row * 2, r);
+                const float mr = recv_ml[(r * 16 + row) * 2];
                 if (mr != -INFINITY) {
                     const float f = fast_exp2(mr - M);
-                    L += ld_cluster_f32(fin_ml + row * 2 + 1, r) * f;
-                    acc += ld_cluster_f32(fin_o + row * HD + d, r) * f;
+                    L += recv_ml[(r * 16 + row) * 2 + 1] * f;
+                    acc += recv_o[r * share + (idx - lo_i)] * f;
                 }
             }
             out[((size_t)t * nh + kh * g + row) * HD + d] = __float2bfloat16_rn((L > 0.f && !dead) ? acc / L : 0.f);
         }
     }
-    cluster_sync_all();              // nobody leaves while others still read its shared memory
 }
 
 // ------------------------------------------------------------------------------------------ prefill
@@ -751,7 +758,8 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
     const int stages = TMA_STAGES_MANY;
     const int nt = g <= 8 ? 1 : 2;                               // tiles of 8 query heads
     const size_t smem = (size_t)stages * 2 * MMA_BN * hd * 2 + (size_t)16 * (hd + 8) * 2 + 2 * stages * 8 + 8 +
-                        TMA_TABLE_CACHE * 4 + 1024;
+                        TMA_TABLE_CACHE * 4 + 1024 +
+                        (n_splits > 1 ? (size_t)(n_splits * ((g * hd + n_splits - 1) / n_splits) + n_splits * 32) * 4 : 0);
     CUtensorMap km, vm;
     memcpy(&km, k_map, sizeof(CUtensorMap));
     memcpy(&vm, v_map, sizeof(CUtensorMap));
