@@ -7,10 +7,12 @@
 // producer warp issues the copies (cp.async.bulk.tensor.3d, completion on an mbarrier) while four
 // consumer warps multiply, so neither the per-16-byte address arithmetic of a cp.async pipeline -
 // which made the earlier kernel instruction-bound - nor the issue of the copies sits in the
-// consumers' way; full/empty mbarriers per stage replace block-wide barriers.  Everything else is
-// as in attention_mma.cu: the g <= 16 query heads of a key/value head form one 16-row tile,
-// mma.sync m16n8k16 with float32 accumulation, running max/sum softmax in float32, the key range
-// of a token cut into n_splits parts whose partial results a second kernel combines.
+// consumers' way; full/empty mbarriers per stage replace block-wide barriers.  The products are
+// mma.sync m16n8k16 with float32 accumulation, with the 16 cache positions of a warp as the rows and
+// the g <= 16 query heads of a key/value head as the 8-wide columns; running max/sum softmax in
+// float32; the key range of a token is cut into n_splits parts, which for 2, 4, 8 or 16 parts form a
+// thread-block cluster that adds its partial results through distributed shared memory (otherwise a
+// second kernel combines them).
 //
 // Formulas restated from the reference as cited in attention_mma.cu
 // (pico_vllm/kernels/attention.py:31, 67-82, 92).  Every wait on an mbarrier is bounded: after
@@ -19,9 +21,7 @@
 #include <cuda.h>
 #include "mma_helpers.cuh"
 
-#define TMA_STAGES_FEW 4
-// stages when there is at most one block per SM (it must keep the SM's loads in flight alone)
-#define TMA_STAGES_MANY 3      // stages with two blocks per SM
+#define TMA_STAGES_MANY 3      // stages of 32 KB: small enough that the next kernel's blocks fit beside a block
 #define TMA_WAIT_LIMIT (1 << 22)
 #ifndef TMA_L2_PROMO
 #define TMA_L2_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
@@ -55,13 +55,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-        : "memory");
-}
-
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -75,13 +68,6 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
-    uint32_t raddr;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(raddr) : "r"(smem_u32(local)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(raddr) : "memory");
-    return v;
 }
 __device__ __forceinline__ void st_cluster_f32(float* local, int rank, float v) {
     uint32_t raddr;
@@ -106,10 +92,8 @@ __device__ __forceinline__ uint32_t swz_addr(uint32_t tile, int key, int dim) {
 // 4 consumer warps (multiply) + 1 producer warp (one lane issues the TMA copies).  full[s]: the
 // copies of stage s have landed (transaction count); empty[s]: the four consumer warps are done
 // with stage s.
-#define TMA_THREADS 160
 // CW consumer warps in groups of four: group i takes tiles i, i + CW/4, ... (a group multiplies one tile,
-// 16 cache positions per warp).  One group is latency-bound at about 0.8 us per tile, so with one
-// block per SM two groups are used; with two blocks per SM one group each.
+// 16 cache positions per warp); one group is what the launcher uses.
 template <int HD, int TMA_STAGES, int CW, int NT>     // head size 64 or 128; stages; consumer warps (4 or 8); 8-head tiles (g <= 8 NT)
 __global__ void __launch_bounds__((CW + 1) * 32)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
@@ -436,214 +420,6 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
     }
 }
 
-// ------------------------------------------------------------------------------------------ prefill
-// Portions of prompts with TMA-fed tiles.  grid: (tiles of tokens, kv heads, listed segments).  A
-// block takes 64 / g tokens of one segment and the g query heads of one kv head: 64 rows, 16 per
-// consumer warp; a fifth warp issues the copies.  Tiles of 64 cache positions, aligned to
-// multiples of 64, from the first visible key of the tile's first token to the last token's own.
-#define PF_STAGES 2
-template <int HD>
-__global__ void __launch_bounds__(TMA_THREADS)
-paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
-                         const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
-                         const int* __restrict__ seg_list, const int* __restrict__ cu_q,
-                         const int* __restrict__ positions, const int* __restrict__ block_table, int table_stride,
-                         int nh, int nkv, int page_size, int window, float scale_log2) {
-    pdl_launch_dependents();
-    extern __shared__ unsigned char smem_dyn[];
-    constexpr int TILE_BYTES = MMA_BN * HD * 2;
-    constexpr int QLD = HD + 8;
-    unsigned char* smem_raw = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-    unsigned char* tiles = smem_raw;                                                  // [stages][K | V]
-    bf16* q_s = reinterpret_cast<bf16*>(smem_raw + PF_STAGES * 2 * TILE_BYTES);       // [64][QLD]
-    uint64_t* full = reinterpret_cast<uint64_t*>(q_s + 64 * QLD);
-    uint64_t* empty = full + PF_STAGES;
-    volatile int* abort_s = reinterpret_cast<volatile int*>(empty + PF_STAGES);
-    int* tbl_s = const_cast<int*>(abort_s) + 2;                                       // [TMA_TABLE_CACHE]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = nh / nkv;
-    const int tpt = 64 / g;
-    const int kh = blockIdx.y;
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < PF_STAGES; ++s) {
-            mbar_init(full + s, 1);
-            mbar_init(empty + s, 4);
-        }
-        *abort_s = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    }
-    pdl_wait();
-    const int seg = seg_list ? seg_list[blockIdx.z] : blockIdx.z;
-    const int q0 = cu_q[seg], qlen = cu_q[seg + 1] - q0;
-    const int tok0 = blockIdx.x * tpt;
-    if (tok0 >= qlen) return;                                    // uniform for the block
-    const int ntok = min(tpt, qlen - tok0);
-    const int pos0 = positions[q0] + tok0;                       // position of the tile's first token
-    const int hi = pos0 + ntok;                                  // one past the last visible key of the tile
-    const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
-    const int t_begin = lo / MMA_BN, t_end = (hi + MMA_BN - 1) / MMA_BN;
-    const int ntiles = t_end - t_begin;
-    const int* table = block_table + (size_t)seg * table_stride;
-    const int ppt = MMA_BN / page_size;
-    {
-        const int first_entry = t_begin * ppt;
-        const int n_entries = min(ntiles * ppt, TMA_TABLE_CACHE);
-        for (int i = threadIdx.x; i < n_entries; i += TMA_THREADS)
-            tbl_s[i] = first_entry + i < table_stride ? table[first_entry + i] : 0;
-    }
-    __syncthreads();
-
-    if (warp == 4) {
-        if (lane == 0) {
-            for (int it = 0; it < ntiles; ++it) {
-                const int s = it % PF_STAGES;
-                if (it >= PF_STAGES && !mbar_wait(empty + s, ((it / PF_STAGES) - 1) & 1)) {
-                    g_tma_status = 1;
-                    *abort_s = 1;
-                }
-                if (*abort_s) break;
-                const int n0 = (t_begin + it) * MMA_BN;
-                unsigned char* kt = tiles + (size_t)s * 2 * TILE_BYTES;
-                unsigned char* vt = kt + TILE_BYTES;
-                int first = 0, last = ppt;
-                while (first < last && n0 + (first + 1) * page_size <= lo) ++first;
-                while (last > first && n0 + (last - 1) * page_size >= hi) --last;
-                mbar_expect_tx(full + s, (uint32_t)((last - first) * page_size * HD * 2 * 2));
-                for (int pg = first; pg < last; ++pg) {
-                    const int e = it * ppt + pg;
-                    const int page = e < TMA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
-                    const int row = (page * nkv + kh) * page_size;
-                    tma_load_3d(kt + pg * page_size * HD * 2, &k_map, 0, 0, row, full + s);
-                    tma_load_3d(vt + pg * page_size * HD * 2, &v_map, 0, 0, row, full + s);
-                }
-            }
-        }
-        return;
-    }
-    // queries of the tile -> shared memory (rows beyond the tile's tokens are zero)
-    for (int idx = threadIdx.x; idx < 64 * (HD / 8); idx += 128) {
-        const int r = idx / (HD / 8), c = idx - r * (HD / 8);
-        const int tok = r / g, head = r - tok * g;
-        const bool ok = tok < ntok;
-        const bf16* src = q + (size_t)(q0 + tok0 + (ok ? tok : 0)) * q_row_stride + (size_t)(kh * g + head) * HD + c * 8;
-        cp_async_16(smem_u32(q_s + r * QLD + c * 8), src, ok);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    consumer_sync<128>();
-
-    float o[HD / 8][4];
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    int row_pos[2], row_lo[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = warp * 16 + (lane >> 2) + r * 8;
-        const int tok = row / g;
-        row_pos[r] = tok < ntok ? pos0 + tok : -1;               // -1: a padding row sees nothing
-        row_lo[r] = (window > 0 && row_pos[r] + 1 > window) ? row_pos[r] + 1 - window : 0;
-    }
-    // what the rows of this warp see: nothing at or beyond warp_hi; everything in [warp_full_lo, warp_full_hi)
-    const int first_tok = (warp * 16) / g, last_tok = min(ntok - 1, (warp * 16 + 15) / g);
-    const bool warp_has_rows = first_tok < ntok;
-    const int warp_hi = warp_has_rows ? pos0 + last_tok + 1 : lo;
-    const bool no_pad_rows = (warp * 16 + 15) / g < ntok;
-    const int warp_full_hi = no_pad_rows ? pos0 + first_tok + 1 : lo;        // keys below are visible to all rows
-    const int warp_full_lo = (window > 0 && pos0 + last_tok + 1 > window) ? pos0 + last_tok + 1 - window : 0;
-    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
-    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
-    const int v_row = (lane & 7) + ((lane >> 3) & 1) * 8, v_col = (lane >> 4) * 8;
-
-    for (int it = 0; it < ntiles; ++it) {
-        const int s = it % PF_STAGES;
-        const int n0 = (t_begin + it) * MMA_BN;
-        if (!mbar_wait(full + s, (it / PF_STAGES) & 1)) {
-            g_tma_status = 1;
-            *abort_s = 1;
-        }
-        if (*abort_s) break;
-        const uint32_t kt = smem_u32(tiles + (size_t)s * 2 * TILE_BYTES);
-        const uint32_t vt = kt + TILE_BYTES;
-        if (n0 < warp_hi) {
-            float sc[MMA_BN / 8][4];
-#pragma unroll
-            for (int j = 0; j < MMA_BN / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
-#pragma unroll
-            for (int k0 = 0; k0 < HD; k0 += 16) {
-                uint32_t a[4];
-                ldmatrix_x4(a, smem_u32(q_s + (warp * 16 + a_row) * QLD + k0 + a_col));
-#pragma unroll
-                for (int j = 0; j < MMA_BN / 8; j += 2) {
-                    uint32_t b[4];
-                    ldmatrix_x4(b, swz_addr<HD>(kt, j * 8 + b_row, k0 + b_col));
-                    mma_bf16(sc[j], a, b[0], b[1]);
-                    mma_bf16(sc[j + 1], a, b[2], b[3]);
-                }
-            }
-            const bool inner = n0 >= warp_full_lo && n0 + MMA_BN <= warp_full_hi;   // every key visible to every row
-            if (inner) {
-#pragma unroll
-                for (int j = 0; j < MMA_BN / 8; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) sc[j][e] *= scale_log2;
-            } else {
-#pragma unroll
-                for (int j = 0; j < MMA_BN / 8; ++j)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int n = n0 + j * 8 + (lane & 3) * 2 + (e & 1);
-                        const int r = e >> 1;
-                        sc[j][e] = (n <= row_pos[r] && n >= row_lo[r]) ? sc[j][e] * scale_log2 : -INFINITY;
-                    }
-            }
-            online_softmax<HD, MMA_BN / 8>(sc, m, l, o);
-            // value rows outside [lo, hi) may hold anything (pages given back, or what lies beyond the
-            // request's last token): they are read as zero
-            const bool v_edge = n0 < lo || n0 + MMA_BN > hi;
-#pragma unroll
-            for (int kk = 0; kk < MMA_BN / 16; ++kk) {
-                uint32_t a[4];
-                a[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
-                a[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
-                a[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
-                a[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
-#pragma unroll
-                for (int d0 = 0; d0 < HD; d0 += 16) {
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, swz_addr<HD>(vt, kk * 16 + v_row, d0 + v_col));
-                    if (v_edge) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int key0 = n0 + kk * 16 + (j & 1) * 8 + (lane & 3) * 2;
-                            const bool ok0 = key0 >= lo && key0 < hi, ok1 = key0 + 1 >= lo && key0 + 1 < hi;
-                            b[j] &= (ok0 ? 0x0000ffffu : 0u) | (ok1 ? 0xffff0000u : 0u);
-                        }
-                    }
-                    mma_bf16(o[d0 / 8], a, b[0], b[1]);
-                    mma_bf16(o[d0 / 8 + 1], a, b[2], b[3]);
-                }
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
-    }
-    if (*abort_s) return;
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = warp * 16 + (lane >> 2) + r * 8;
-        const int tok = row / g, head = row - tok * g;
-        if (tok >= ntok) continue;
-        const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
-        bf16* dst = out + ((size_t)(q0 + tok0 + tok) * nh + kh * g + head) * HD + (lane & 3) * 2;
-#pragma unroll
-        for (int i = 0; i < HD / 8; ++i)
-            *reinterpret_cast<__nv_bfloat162*>(dst + i * 8) = __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
-    }
-}
-
 // ------------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -728,16 +504,6 @@ static bool tma_cluster_ok(int hd, int size, int nt, size_t smem) {
     return c == 1;
 }
 
-static int tma_num_sms() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
-
 // Single tokens with TMA-fed tiles.  k_map / v_map: tensor maps made by pico_make_kv_tensor_map (host
 // pointers; they are copied into the kernel's parameters).  Other arguments as pico_paged_decode_mma.
 PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const void* q, int q_row_stride, void* out,
@@ -785,37 +551,5 @@ PICO_API int pico_paged_decode_tma(const void* k_map, const void* v_map, const v
 #undef LAUNCH_TMA
     if (n_splits > 1 && !cluster)
         return pico_launch_decode_combine(part_o, part_ml, out, tok_list, n_tok, nh, hd, n_splits, stream);
-    return pico_launch_status();
-}
-
-// Prompt portions with TMA-fed tiles; arguments as pico_paged_prefill_mma plus the tensor maps.
-PICO_API int pico_paged_prefill_tma(const void* k_map, const void* v_map, const void* q, int q_row_stride, void* out,
-                                    const int* seg_list, int n_segs, const int* cu_q, int max_q_len,
-                                    const int* positions, const int* block_table, int table_stride, int nh, int nkv,
-                                    int hd, int page_size, int window, float scale, cudaStream_t stream) {
-    if (n_segs <= 0 || max_q_len <= 0) return 0;
-    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
-    const int g = nh / nkv;
-    if (g > 64 || nkv > 65535 || n_segs > 65535) return PICO_ERR_SIZE;
-    if (page_size < 8 || MMA_BN % page_size != 0) return PICO_ERR_SIZE;
-    if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
-    const int tpt = 64 / g;
-    const dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_segs);
-    const float scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)PF_STAGES * 2 * MMA_BN * hd * 2 + (size_t)64 * (hd + 8) * 2 + 2 * PF_STAGES * 8 + 8 +
-                        TMA_TABLE_CACHE * 4 + 1024;
-    CUtensorMap km, vm;
-    memcpy(&km, k_map, sizeof(CUtensorMap));
-    memcpy(&vm, v_map, sizeof(CUtensorMap));
-#define LAUNCH_PF_TMA(HD)                                                                                            \
-    do {                                                                                                             \
-        cudaFuncSetAttribute(paged_prefill_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-        pico_launch((paged_prefill_tma_kernel<HD>), grid, dim3(TMA_THREADS), smem, stream, km, vm, (const bf16*)q,   \
-                    q_row_stride, (bf16*)out, seg_list, cu_q, positions, block_table, table_stride, nh, nkv,         \
-                    page_size, window, scale_log2);                                                                  \
-    } while (0)
-    if (hd == 64) LAUNCH_PF_TMA(64);
-    else LAUNCH_PF_TMA(128);
-#undef LAUNCH_PF_TMA
     return pico_launch_status();
 }

@@ -64,7 +64,6 @@ def library():
         "pico_make_kv_tensor_map": [vp, vp, i64, i32, i32],
         "pico_paged_decode_tma": [vp, vp, vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                                   f32, i32, vp],
-        "pico_paged_prefill_tma": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
         "pico_tma_status": [vp],
         "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32, i32],
         "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
@@ -341,20 +340,12 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
             raise KernelError("paged_attention_mma: index tensors must be int32")
     lib = library()
     win = int(window) if window else 0
-    use_tma = k_map is not None and v_map is not None
     if n_prefill_segs > 0 and k_map2d is not None and v_map2d is not None:
         _check(lib.pico_paged_prefill_tcgen05(k_map2d[1], v_map2d[1], _ptr(q), q.stride(0), _ptr(out),
                                               _ptr(prefill_segs), n_prefill_segs, _ptr(cu_q), max_prefill_q,
                                               _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
                                               n_kv_heads, head_dim, page_size, win, float(scale), _stream()),
                f"paged_prefill_tcgen05 (head_dim {head_dim})")
-        _count()
-    elif n_prefill_segs > 0 and use_tma and n_heads // n_kv_heads <= 64:
-        _check(lib.pico_paged_prefill_tma(k_map[1], v_map[1], _ptr(q), q.stride(0), _ptr(out), _ptr(prefill_segs),
-                                          n_prefill_segs, _ptr(cu_q), max_prefill_q, _ptr(positions),
-                                          _ptr(block_table), block_table.stride(0), n_heads, n_kv_heads, head_dim,
-                                          page_size, win, float(scale), _stream()),
-               f"paged_prefill_tma (head_dim {head_dim})")
         _count()
     elif n_prefill_segs > 0:
         _check(lib.pico_paged_prefill_mma(_ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out),

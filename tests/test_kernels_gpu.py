@@ -260,13 +260,6 @@ def test_tcgen05_prefill_far_key_and_window_edge(window, q_lens):
     assert torch.allclose(got, want, **MMA_TOL)
 
 
-@pytest.mark.parametrize("window,q_lens", [(None, [200, 150]), (64, [200, 150]), (None, [2, 300]), (100, [517, 64])])
-def test_tma_prefill_far_key_and_window_edge(window, q_lens):
-    got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=q_lens, splits=1,
-                                seed=5, spike=True, mma=True, tma=True, poison=True)
-    assert torch.allclose(got, want, **MMA_TOL)
-
-
 @pytest.mark.parametrize("window,splits", [(None, 1), (None, 8), (64, 1), (64, 4)])
 def test_tma_decode_far_key_and_window_edge(window, splits):
     got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=[1, 1], splits=splits,
