@@ -69,6 +69,27 @@ def test_long_decoding(dtype, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_long_prompts_in_one_step(dtype, name):
+    """Prompts of several hundred tokens, whole and as two requests in one step: in bfloat16 these
+    sizes go through the tcgen05 kernels (products from 128 tokens on, pairs of SMs from 256 on,
+    attention tiles of 128 rows with several key tiles)."""
+    cfg = helpers.tiny_config(name)
+    reqs = {"x": helpers.random_ids(700, cfg.vocab_size, 31), "y": helpers.random_ids(300, cfg.vocab_size, 32)}
+    steps = [dict(entries=[dict(id="x", tokens=reqs["x"], want=list(range(0, 700, 7)))], end=["x"]),
+             dict(entries=[dict(id="x", tokens=reqs["x"][:450], want=[0, 449]),
+                           dict(id="y", tokens=reqs["y"], want=list(range(0, 300, 3)))], end=["y"]),
+             dict(entries=[dict(id="x", tokens=reqs["x"][450:], want=list(range(0, 250, 5)))], end=["x"])]
+    runner, tensors = helpers.make_runner_from_tensors(name, dtype, DEV, 1100)
+    want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
+    for i, (g, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+        assert torch.isfinite(g).all()
+        helpers.assert_close_logits(g, w, REL[dtype], f"{name}/{dtype} step {i}")
+    from pico_vllm_b200 import ops
+    assert ops.tc_status() == 0 and ops.tca_status() == 0 and ops.tma_status() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(dtype):
     """Position 0 alone, then 1, 2, 3 one by one: the shortest contexts."""
     cfg = helpers.tiny_config("c")
