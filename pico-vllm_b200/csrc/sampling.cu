@@ -1,6 +1,9 @@
-// Next-token choice from float32 logits, one block per row: argmax (temperature 0),
-// temperature sampling, and nucleus (top-p) sampling, by inverse CDF with one uniform number
-// per row that the host supplies.
+// Next-token choice from float32 logits: argmax (temperature 0), temperature sampling, and nucleus
+// (top-p) sampling, by inverse CDF with one uniform number per row that the host supplies.  The
+// maximum of a row and its first index are found by several blocks (a vocabulary of 150 k entries is
+// 600 KB per row: one block per row took 63 us for 8 rows); the block that finishes a row last adds
+// up the partial results - in the order of the parts, so the result does not depend on which block
+// that is - and, for a row that is sampled, goes on alone with the passes over the row.
 //
 // Restated from the reference: temperature 0 means argmax (pico_vllm/sampler.py:3-8,62-63);
 // otherwise probabilities are softmax(logits / temperature) (sampler.py:16); top-p keeps, in
@@ -46,23 +49,62 @@ __device__ __forceinline__ float block_excl_scan(float v, float* scratch, float*
     return res;
 }
 
+#define SAMPLE_MAX_PARTS 64
+#define SAMPLE_MAX_ROWS 1024
+__device__ float g_sample_part_max[SAMPLE_MAX_ROWS * SAMPLE_MAX_PARTS];
+__device__ int g_sample_part_arg[SAMPLE_MAX_ROWS * SAMPLE_MAX_PARTS];
+__device__ int g_sample_arrived[SAMPLE_MAX_ROWS];
+
+// grid (parts, rows): block (p, r) takes elements [p * per, (p + 1) * per) of row r
 __global__ void sample_kernel(const float* __restrict__ logits, int row_stride, int V,
                               const float* __restrict__ temperature, const float* __restrict__ top_p,
-                              const float* __restrict__ uniform, int* __restrict__ out) {
+                              const float* __restrict__ uniform, int* __restrict__ out, int per) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[33];
     __shared__ int iscratch[33];
-    const int r = blockIdx.x;
+    const int r = blockIdx.y, parts = gridDim.x;
     const float* x = logits + (size_t)r * row_stride;
     const int tid = threadIdx.x;
 
-    // max and its first index
+    // max and its first index, of this block's part
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < V; i += blockDim.x) {
-        const float v = x[i];
-        if (v > best) { best = v; best_i = i; }
+    {
+        const int p0 = min(V, (int)blockIdx.x * per), p1 = min(V, p0 + per);
+        for (int i = p0 + tid; i < p1; i += blockDim.x) {
+            const float v = x[i];
+            if (v > best) { best = v; best_i = i; }
+        }
+    }
+    if (parts > 1) {
+        const float pm = block_max(best, scratch);
+        int pc = (best == pm) ? best_i : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) pc = min(pc, __shfl_xor_sync(0xffffffffu, pc, o));
+        __syncthreads();
+        if ((tid & 31) == 0) iscratch[tid >> 5] = pc;
+        __syncthreads();
+        if (tid == 0) {
+            int c = 0x7fffffff;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) c = min(c, iscratch[w]);
+            g_sample_part_max[r * SAMPLE_MAX_PARTS + blockIdx.x] = pm;
+            g_sample_part_arg[r * SAMPLE_MAX_PARTS + blockIdx.x] = c;
+            __threadfence();
+            iscratch[32] = atomicAdd(&g_sample_arrived[r], 1) == parts - 1;
+        }
+        __syncthreads();
+        if (!iscratch[32]) return;                  // another block finishes this row
+        __threadfence();
+        if (tid == 0) g_sample_arrived[r] = 0;       // for the next launch
+        // the parts in their order: the first index of the maximum stays the first
+        best = -INFINITY;
+        best_i = 0x7fffffff;
+        if (tid < parts) {
+            best = __ldcg(&g_sample_part_max[r * SAMPLE_MAX_PARTS + tid]);
+            best_i = __ldcg(&g_sample_part_arg[r * SAMPLE_MAX_PARTS + tid]);
+        }
+        __syncthreads();
     }
     const float mx = block_max(best, scratch);
     int cand = (best == mx) ? best_i : 0x7fffffff;
@@ -163,7 +205,14 @@ PICO_API int pico_sample(const float* logits, int row_stride, int R, int V, cons
     if (R <= 0) return 0;
     if (V <= 0) return PICO_ERR_SIZE;
     if (temperature && !uniform) return PICO_ERR_SIZE;
-    pico_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, V, temperature, top_p, uniform, out);
+    // parts of at least 2048 entries, as many as give every SM a block or two
+    int parts = 1;
+    if (R <= SAMPLE_MAX_ROWS) {
+        while (parts < SAMPLE_MAX_PARTS && parts * 2 * 2048 <= V && parts * R < 296) parts *= 2;
+    }
+    const int per = (V + parts - 1) / parts;
+    pico_launch(sample_kernel, dim3(parts, R), dim3(SAMPLE_THREADS), 0, stream, logits, row_stride, V, temperature, top_p, uniform,
+                out, per);
     return pico_launch_status();
 }
 
