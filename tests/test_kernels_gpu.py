@@ -34,7 +34,8 @@ def test_embedding(tdtype, T, H, V):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H,eps", [(1, 16, 1e-6), (9, 200, 1e-5), (4, 1000, 1e-3), (3, 5000, 1e-6)])
+@pytest.mark.parametrize("T,H,eps", [(1, 16, 1e-6), (9, 200, 1e-5), (4, 1000, 1e-3), (3, 5000, 1e-6),
+                                     (70, 200, 1e-5), (131, 1536, 1e-6), (65, 3584, 1e-6), (64, 4100, 1e-6), (77, 1100, 1e-4)])
 @pytest.mark.parametrize("with_delta", [False, True])
 def test_add_rmsnorm(dtype, T, H, eps, with_delta):
     from pico_vllm_b200 import ops
