@@ -6,7 +6,8 @@
 //               dims] boxes, one per page and 64-dim block), warp 13 the values (one box per page with all
 //               its 64-dim blocks), 128-byte swizzle, separate rings for keys and values: a key stage is
 //               free once S = Q K^T has read it, a value stage once O += P V has;
-//   warps 1, 10-12  one lane each issues tcgen05.mma: S = Q K^T (M 128, N 64, Q and K from shared memory,
+//   warps 1, 10-12  one lane each issues tcgen05.mma: S = Q K^T (M 128, N 64, Q from tensor memory - the
+//               softmax warps of pipeline 0 put their rows there once -, K from shared memory,
 //               accumulator S in tensor memory) for pipeline 0 (warp 1) and 1 (warp 10); O += P V (M 128,
 //               N head_dim, P read from tensor memory, V from shared memory as an MN-major operand,
 //               accumulator O in tensor memory) for pipeline 0 (warp 11) and 1 (warp 12).  A tcgen05.mma
@@ -170,6 +171,7 @@ __device__ __forceinline__ void tca_softmax_sync() { asm volatile("bar.sync 2, 2
 #define TCA_COL_S 0
 #define TCA_COL_P 128
 #define TCA_COL_O 192
+#define TCA_COL_Q 448          // the queries as a tensor-memory operand: 64 columns of bfloat16 pairs at head size 128
 
 template <int HD>      // head size, a multiple of 64 up to 128
 __global__ void __launch_bounds__(TCA_THREADS)
@@ -183,10 +185,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     constexpr int NH = HD / 64;                              // 64-dim blocks of a head
     constexpr int SUB = TCA_BN * 128;                        // bytes of one [64 keys][64 dims] block
     constexpr int KV_BYTES = NH * SUB;                       // one K (or V) tile
-    constexpr int QSUB = TCA_BM * 128;                       // bytes of one [128 rows][64 dims] block of Q
     unsigned char* smem = tca_dyn + ((1024u - (tca_u32(tca_dyn) & 1023u)) & 1023u);
-    unsigned char* q_s = smem;                               // [NH][128 rows][128 B]
-    unsigned char* k_s = q_s + NH * QSUB;                    // [stages] K tiles: a stage is free once S = Q K^T has read it
+    unsigned char* k_s = smem;                               // [stages] K tiles: a stage is free once S = Q K^T has read it
     unsigned char* v_s = k_s + TCA_STAGES * KV_BYTES;        // [stages] V tiles: free once O += P V has read it, two tiles later
     uint64_t* k_full = reinterpret_cast<uint64_t*>(v_s + TCA_STAGES * KV_BYTES);
     uint64_t* k_empty = k_full + TCA_STAGES;
@@ -196,7 +196,8 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     uint64_t* s_empty = s_full + 2;                          // [2] the softmax warps have read them
     uint64_t* p_full = s_empty + 2;                          // [2] the probabilities are in tensor memory (and O is rescaled)
     uint64_t* pv_done = p_full + 2;                          // [2] the p.v products of a tile are done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+    uint64_t* q_ready = pv_done + 2;                         // the queries are in tensor memory
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 1);
     volatile int* abort_s = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float2* ml_s = reinterpret_cast<float2*>(const_cast<int*>(abort_s) + 3);   // [2][128] maximum in use and sum of a row
     int* tbl_s = reinterpret_cast<int*>(ml_s + 2 * TCA_BM);  // [TCA_TABLE_CACHE]
@@ -218,6 +219,7 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
             tca_mbar_init(p_full + i, 4);
             tca_mbar_init(pv_done + i, 1);
         }
+        tca_mbar_init(q_ready, 4);
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         tca_fence_async();
@@ -245,17 +247,6 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const int n_entries = min(ntiles * ppt, TCA_TABLE_CACHE);
         for (int i = threadIdx.x; i < n_entries; i += TCA_THREADS)
             tbl_s[i] = first_entry + i < table_stride ? table[first_entry + i] : 0;
-        // queries -> shared memory in the operand layout: row r = token * g + head, 16-byte piece c of
-        // block h at q_s + h * QSUB + r * 128 + ((c ^ (r & 7)) << 4); rows beyond the tile are zero
-        for (int idx = threadIdx.x; idx < TCA_BM * (HD / 8); idx += TCA_THREADS) {
-            const int r = idx / (HD / 8), c = idx - r * (HD / 8);
-            const int tok = r / g, head = r - tok * g;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (tok < ntok)
-                v = *reinterpret_cast<const uint4*>(q + (size_t)(q0 + tok0 + tok) * q_row_stride + (size_t)(kh * g + head) * HD + c * 8);
-            *reinterpret_cast<uint4*>(q_s + (c >> 3) * QSUB + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-        }
-        tca_fence_async();       // the tensor core reads Q through the async proxy
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
@@ -313,24 +304,22 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
             bool ok = true;
             // every descriptor is made once: per tile only the stage's offset (in 16-byte units) is added
             if (!is_pv) {
-                uint64_t q_desc[NH * 4], k_desc[NH * 4];
-                const uint32_t qa = tca_u32(q_s), k0 = tca_u32(k_s);
+                uint64_t k_desc[NH * 4];
+                const uint32_t k0 = tca_u32(k_s);
 #pragma unroll
                 for (int h = 0; h < NH; ++h)
 #pragma unroll
-                    for (int k16 = 0; k16 < 4; ++k16) {
-                        q_desc[h * 4 + k16] = tca_desc_k(qa + h * QSUB, k16);
-                        k_desc[h * 4 + k16] = tca_desc_k(k0 + h * SUB, k16);
-                    }
-                const uint32_t ts = tmem_base + TCA_COL_S + pipe * TCA_BN;
+                    for (int k16 = 0; k16 < 4; ++k16) k_desc[h * 4 + k16] = tca_desc_k(k0 + h * SUB, k16);
+                const uint32_t ts = tmem_base + TCA_COL_S + pipe * TCA_BN, tq = tmem_base + TCA_COL_Q;
+                ok = tca_wait(q_ready, 0);
                 int j = 0;
-                for (int it = pipe; it < ntiles; it += 2, ++j) {
+                for (int it = pipe; ok && it < ntiles; it += 2, ++j) {
                     const int s = it % TCA_STAGES;
                     if (!tca_wait(k_full + s, (it / TCA_STAGES) & 1) || (j > 0 && !tca_wait(s_empty + pipe, (j - 1) & 1))) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const uint64_t stage = (uint64_t)(s * (KV_BYTES >> 4));
 #pragma unroll
-                    for (int i = 0; i < NH * 4; ++i) tca_mma(ts, q_desc[i], k_desc[i] + stage, idesc_s, i ? 1u : 0u);
+                    for (int i = 0; i < NH * 4; ++i) tca_mma_ts(ts, tq + i * 8, k_desc[i] + stage, idesc_s, i ? 1u : 0u);
                     tca_commit(k_empty + s);           // the keys of the stage have been read
                     tca_commit(s_full + pipe);
                 }
@@ -376,6 +365,25 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const uint32_t tmem_s = tmem_base + TCA_COL_S + pipe * TCA_BN + lane_off;
         const uint32_t tmem_p = tmem_base + TCA_COL_P + pipe * (TCA_BN / 2) + lane_off;
         const uint32_t tmem_o = tmem_base + TCA_COL_O + pipe * HD + lane_off;
+        if (pipe == 0) {
+            // this thread's query row -> tensor memory, as the a operand of S = Q K^T: column i of the row holds
+            // dims 2i and 2i + 1 (rows beyond the tile's tokens are zero)
+            const bf16* qrow = q + (size_t)(q0 + tok0 + (row_ok ? tok : 0)) * q_row_stride + (size_t)(kh * g + head) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 2; c += 32) {
+                uint32_t qv[32];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 v = row_ok ? *reinterpret_cast<const uint4*>(qrow + c * 2 + i * 8) : make_uint4(0u, 0u, 0u, 0u);
+                    qv[4 * i] = v.x; qv[4 * i + 1] = v.y; qv[4 * i + 2] = v.z; qv[4 * i + 3] = v.w;
+                }
+                tca_st32(tmem_base + TCA_COL_Q + lane_off + c, qv);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tca_arrive(q_ready);
+        }
         float m_use = -INFINITY, l = 0.f;                    // maximum in use (log2 units), running sum
         bool dead = false;
         const uint64_t scale2 = tca_pack(scale_log2, scale_log2);
@@ -597,8 +605,7 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
     const int tpt = TCA_BM / g;
     const dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_segs);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)(hd / 64) * TCA_BM * 128 + (size_t)TCA_STAGES * 2 * TCA_BN * hd * 2 +
-                        (4 * TCA_STAGES + 8) * 8 + 16 + 2 * TCA_BM * 8 + TCA_TABLE_CACHE * 4 + 1024;
+    const size_t smem = (size_t)TCA_STAGES * 2 * TCA_BN * hd * 2 + (4 * TCA_STAGES + 9) * 8 + 16 + 2 * TCA_BM * 8 + TCA_TABLE_CACHE * 4 + 1024;
     CUtensorMap km, vm;
     memcpy(&km, k_map, sizeof(CUtensorMap));
     memcpy(&vm, v_map, sizeof(CUtensorMap));
