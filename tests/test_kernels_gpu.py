@@ -254,6 +254,16 @@ def test_tcgen05_attention_mixed_segments(nh, nkv, hd, ps, window):
     assert torch.allclose(got, want, **MMA_TOL)
 
 
+@pytest.mark.parametrize("window", [None, 5000])
+def test_long_contexts_beyond_the_block_table_cache(window):
+    """Contexts whose block tables are longer than what a block keeps in shared memory (256 entries in
+    the decode kernel, 1024 in the prompt kernel): the entries beyond come straight from global memory."""
+    got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[9100, 6000, 2100], q_lens=[300, 1, 1], splits=1,
+                                seed=7, spike=True, mma=True, tma=True, poison=True, tc=True)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **MMA_TOL)
+
+
 @pytest.mark.parametrize("window,q_lens", [(None, [200, 150]), (64, [200, 150]), (None, [2, 300]), (100, [517, 64])])
 def test_tcgen05_prefill_far_key_and_window_edge(window, q_lens):
     got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=q_lens, splits=1,
