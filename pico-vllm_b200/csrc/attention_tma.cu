@@ -22,7 +22,7 @@
 #include "mma_helpers.cuh"
 
 #define TMA_STAGES_MANY 3      // stages of 32 KB: small enough that the next kernel's blocks fit beside a block
-#define TMA_WAIT_LIMIT (1 << 22)
+#define TMA_WAIT_LIMIT (1 << 15)     // polls of a barrier (some microseconds each) before a thread gives up
 #ifndef TMA_L2_PROMO
 #define TMA_L2_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
 #endif
