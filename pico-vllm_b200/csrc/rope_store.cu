@@ -68,9 +68,11 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const fl
 }
 
 // The same for bfloat16 with 16-byte accesses: a thread takes 8 consecutive pairs (dims i..i+7 and
-// i + hd/2 .. of one head) or 8 consecutive dims of a value head; a block takes ROPE_TPB tokens.
+// i + hd/2 .. of one head) or 8 consecutive dims of a value head; a block takes `tpb` tokens (as many as
+// give it about 256 threads' worth of work; one token with 160 threads at 12 + 2 heads of 128, which
+// measured fastest of the block shapes tried).
 // Needs hd % 16 == 0, rot_half % 8 == 0, row_stride % 8 == 0 and 16-byte aligned buffers.
-#define ROPE_TPB 4
+#define ROPE_MAX_TPB 8
 __device__ __forceinline__ void rope_unpack8(const uint4& v, float (&f)[8]) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -97,12 +99,12 @@ __global__ void __launch_bounds__(256)
 rope_store_bf16x8_kernel(bf16* __restrict__ qkv, int row_stride, const float* __restrict__ bias,
                          const int* __restrict__ positions, const float* __restrict__ inv_freq,
                          const int* __restrict__ slots, bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int T,
-                         int nh, int nkv, int hd, int rot_half, int page_size) {
+                         int nh, int nkv, int hd, int rot_half, int page_size, int tpb) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float cs[];  // [ROPE_TPB][cos[rot_half], sin[rot_half]]
-    const int t0 = blockIdx.x * ROPE_TPB;
-    for (int idx = threadIdx.x; idx < ROPE_TPB * rot_half; idx += blockDim.x) {
+    extern __shared__ float cs[];  // [tpb][cos[rot_half], sin[rot_half]]
+    const int t0 = blockIdx.x * tpb;
+    for (int idx = threadIdx.x; idx < tpb * rot_half; idx += blockDim.x) {
         const int tt = idx / rot_half, i = idx - tt * rot_half;
         if (t0 + tt < T) {
             float s, c;
@@ -114,7 +116,7 @@ rope_store_bf16x8_kernel(bf16* __restrict__ qkv, int row_stride, const float* __
     __syncthreads();
     const int half = hd / 2, gph = half / 8;               // groups of 8 pairs per head
     const int rot_items = (nh + nkv) * gph, v_items = nkv * (hd / 8), items = rot_items + v_items;
-    for (int idx = threadIdx.x; idx < ROPE_TPB * items; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < tpb * items; idx += blockDim.x) {
         const int tt = idx / items, w = idx - tt * items;
         const int t = t0 + tt;
         if (t >= T) break;
@@ -173,12 +175,17 @@ PICO_API int pico_rope_store(void* qkv, int row_stride, const float* bias, const
     const bool vec = act_dtype == PICO_BF16 && hd % 16 == 0 && rot_half % 8 == 0 && row_stride % 8 == 0 &&
                      ((uintptr_t)qkv & 15) == 0 && (!bias || ((uintptr_t)bias & 15) == 0) &&
                      (!slots || (((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0)) &&
-                     (size_t)ROPE_TPB * smem <= 48 * 1024;
-    if (vec)
-        pico_launch(rope_store_bf16x8_kernel, dim3((T + ROPE_TPB - 1) / ROPE_TPB), dim3(256), (size_t)ROPE_TPB * smem, stream,
+                     (size_t)ROPE_MAX_TPB * smem <= 48 * 1024;
+    if (vec) {
+        const int items = (nh + nkv) * (hd / 16) + nkv * (hd / 8);      // 16-byte pieces of work per token
+        int tpb = 256 / items;
+        tpb = tpb < 1 ? 1 : (tpb > ROPE_MAX_TPB ? ROPE_MAX_TPB : tpb);
+        int vthreads = (tpb * items + 31) / 32 * 32;
+        vthreads = vthreads > 256 ? 256 : vthreads;
+        pico_launch(rope_store_bf16x8_kernel, dim3((T + tpb - 1) / tpb), dim3(vthreads), (size_t)tpb * smem, stream,
                     (bf16*)qkv, row_stride, bias, positions, inv_freq, slots, (bf16*)k_pages, (bf16*)v_pages, T, nh, nkv, hd,
-                    rot_half, page_size);
-    else if (act_dtype == PICO_F32)
+                    rot_half, page_size, tpb);
+    } else if (act_dtype == PICO_F32)
         pico_launch((rope_store_kernel<float>), dim3(T), dim3(threads), smem, stream, (float*)qkv, row_stride, bias, positions, inv_freq,
                                                                slots, (float*)k_pages, (float*)v_pages, nh, nkv, hd,
                                                                rot_half, page_size);
