@@ -119,7 +119,7 @@ PICO_API int pico_add_rmsnorm(float* x, const void* delta, const float* weight, 
     if (smem > 200 * 1024) return PICO_ERR_SIZE;
     int threads = 256;
     if (H <= 256) threads = 64;
-    else if (H <= 1024) threads = 128;
+    else if (H <= 2048) threads = 128;       // 128 threads were faster than 192, 256 and 384 at 2048 rows of 1536
     else if (H > 4096) threads = 512;
 #define LAUNCH_NORM(TA, V4)                                                                                          \
     do {                                                                                                             \
