@@ -94,7 +94,9 @@ def _check(code: int, what: str) -> None:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The current CUDA stream's handle (the raw getter: torch.cuda.current_stream() costs ~14 us a call,
+    which at ten launches a layer was a third of a step's host time)."""
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def _cuda(*tensors) -> None:
