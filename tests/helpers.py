@@ -1,4 +1,4 @@
-"""Shared by the tests: the two tiny configurations, model folders, and the four ways of
+"""Shared by the tests: the tiny configurations, model folders, and the four ways of
 cutting requests into steps."""
 import json
 import os
@@ -28,6 +28,18 @@ TINY = {
                        rope_theta=50000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
                        max_position_embeddings=1024),
               page_size=4, seed=303),
+    # D and E: the head sizes of the served models (64 and 128), which the TMA decode kernel and the tcgen05
+    # prefill kernel take; D with a window in its second layer, E with three query heads on one kv head
+    "d": dict(raw=dict(architectures=["Qwen2ForCausalLM"], vocab_size=300, hidden_size=256, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, intermediate_size=384, rope_theta=1000000.0,
+                       rms_norm_eps=1e-6, tie_word_embeddings=True, use_sliding_window=True, sliding_window=40,
+                       max_window_layers=1, max_position_embeddings=4096),
+              page_size=16, seed=404),
+    "e": dict(raw=dict(architectures=["Qwen2ForCausalLM"], vocab_size=411, hidden_size=192, num_hidden_layers=2,
+                       num_attention_heads=3, num_key_value_heads=1, head_dim=128, intermediate_size=272,
+                       rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                       max_position_embeddings=2048),
+              page_size=32, seed=505),
 }
 
 

@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
 REL = {"float32": 5e-5, "bfloat16": 3e-2}     # max |difference| / max |logit| over a step
-LENGTHS = {"a": [5, 17, 33, 70, 150], "b": [1, 9, 24, 40, 77, 131], "c": [3, 21, 50, 97]}
+LENGTHS = {"a": [5, 17, 33, 70, 150], "b": [1, 9, 24, 40, 77, 131], "c": [3, 21, 50, 97],
+           "d": [4, 30, 66, 129, 200], "e": [2, 19, 65, 140]}
 
 
 def _requests(name, vocab):
@@ -30,7 +31,7 @@ _CUTS = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_tail_deco
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
 @pytest.mark.parametrize("graph", [False, True])
 def test_every_cutting_matches_plain(dtype, name, cut, graph):
@@ -54,7 +55,7 @@ def test_every_cutting_matches_plain(dtype, name, cut, graph):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "d"])
 def test_long_decoding(dtype, name):
     """A short prompt, then 400 tokens one by one (pages fill up, the window moves on)."""
     cfg = helpers.tiny_config(name)
@@ -69,7 +70,7 @@ def test_long_decoding(dtype, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "d", "e"])
 def test_long_prompts_in_one_step(dtype, name):
     """Prompts of several hundred tokens, whole and as two requests in one step: in bfloat16 these
     sizes go through the tcgen05 kernels (products from 128 tokens on, pairs of SMs from 256 on,
