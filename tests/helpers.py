@@ -9,13 +9,13 @@ import plain_qwen2 as plain
 
 # Two tiny configurations that differ in every size and option.
 TINY = {
-    # A: BASELINE "Tiny Qwen2 A" - tied head, no window, page 16
+    # A: 2 layers, width 64, 4 heads on 2 kv heads of 16, tied head, no window, page 16
     "a": dict(raw=dict(architectures=["Qwen2ForCausalLM"], vocab_size=256, hidden_size=64, num_hidden_layers=2,
                        num_attention_heads=4, num_key_value_heads=2, intermediate_size=128, rope_theta=10000.0,
                        rms_norm_eps=1e-6, tie_word_embeddings=True, use_sliding_window=False,
                        max_position_embeddings=2048),
               page_size=16, seed=101),
-    # B: BASELINE "Tiny Qwen2 B" sizes (none a power of two), untied head, page 8, and - so that the
+    # B: 3 layers, width 192, 6 heads on 3 kv heads of 32 (sizes that are no power of two), untied head, page 8, and - so that the
     # two differ in every option - a window of 24 keys in the layers from index 1 on
     "b": dict(raw=dict(architectures=["Qwen2ForCausalLM"], vocab_size=512, hidden_size=192, num_hidden_layers=3,
                        num_attention_heads=6, num_key_value_heads=3, intermediate_size=320, rope_theta=1000000.0,

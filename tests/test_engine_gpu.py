@@ -1,6 +1,7 @@
 """The engine on the GPU against the plain implementation, in 32-bit and in bfloat16: every
 way of cutting requests into steps, long decoding, first tokens, generation through the entry
-point, graph replay, parts alone, and a toy mixer with state of its own."""
+point, graph replay, parts alone, and toy parts defined here (a mixer with state of its own, a
+feed-forward with routing, another position encoding)."""
 import math
 
 import pytest
@@ -334,3 +335,126 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped():
     toy.decay = 0.5
     other = helpers.replay(runner, helpers.trace_whole({"p": ids["p"]}))[0]
     assert float((other - ref["p"]).abs().max()) > 1e-3
+
+
+# ------------------------------------------- a toy feed-forward with routing, a toy position encoding
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding():
+    """Two more parts defined here and registered without a change to the package: a feed-forward
+    that routes each token to one of three small gated experts (router logits in float32), and a
+    rotary encoding whose angles run at a third of the speed.  A model of two blocks - attention
+    with the slow rotation + the experts; windowed attention + the ordinary feed-forward - is
+    stepped whole and in mixed portions and compared with the same model written out here with
+    the plain functions."""
+    from pico_vllm_b200.parts import (Part, Param, Piece, register, make, PreNormBlock, RMSNorm, GatedMLP,
+                                      GQAAttention, Rotary, TokenEmbedding, OutputHead)
+    from pico_vllm_b200.models import DecoderModel, LayerCall, Binding
+    from pico_vllm_b200.config import EngineConfig
+    from pico_vllm_b200.engine import ModelRunner, make_cache
+    from pico_vllm_b200.weights import load_state_dict
+
+    @register("feed_forward", "toy_top1_experts")
+    class Top1Experts(Part):
+        def __init__(self, width, inner, experts):
+            self.width, self.inner, self.experts = width, inner, experts
+            self.router = self.gate_up = self.down = None
+
+        def params(self):
+            E, I, W = self.experts, self.inner, self.width
+            return [Param("router", (Piece("router", (E, W)),)),
+                    Param("gate_up", tuple(Piece(f"e{e}.{n}", (I, W)) for e in range(E) for n in ("gate", "up"))),
+                    Param("down", tuple(Piece(f"e{e}.down", (W, I)) for e in range(E)))]
+
+        def forward(self, h, batch):
+            I, W = self.inner, self.width
+            choice = (h.float() @ self.router.float().t()).argmax(-1)
+            out = torch.zeros_like(h)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    x = h[rows].float()
+                    g = x @ self.gate_up[2 * e * I:(2 * e + 1) * I].float().t()
+                    u = x @ self.gate_up[(2 * e + 1) * I:(2 * e + 2) * I].float().t()
+                    out[rows] = ((g * torch.sigmoid(g) * u) @ self.down[e * W:(e + 1) * W].float().t()).to(h.dtype)
+            return out
+
+    @register("position", "toy_slow_rotary")
+    class SlowRotary(Rotary):
+        def __init__(self, head_dim, theta, slowdown):
+            super().__init__(head_dim, theta)
+            self.slowdown = slowdown
+
+        def frequencies(self):
+            return super().frequencies() / self.slowdown
+
+    W, V, I, E, hd = 48, 61, 40, 3, 16
+    embed = TokenEmbedding(V, W)
+    experts = make("feed_forward", "toy_top1_experts", width=W, inner=24, experts=E)
+    slow = make("position", "toy_slow_rotary", head_dim=hd, theta=300.0, slowdown=3.0)
+    blocks = [PreNormBlock(RMSNorm(W, 1e-5), GQAAttention(W, 3, 1, hd, position=slow), RMSNorm(W, 1e-5), experts),
+              PreNormBlock(RMSNorm(W, 1e-6), GQAAttention(W, 2, 2, hd, position=Rotary(hd, 5000.0), window=9),
+                           RMSNorm(W, 1e-6), GatedMLP(W, I))]
+    bindings = [Binding(embed, {"weight": "emb"})]
+    for i, b in enumerate(blocks):
+        for pn, part in b.parts().items():
+            bindings.append(Binding(part, {pc.key: f"l{i}.{pn}.{pc.key}" for p in part.params() for pc in p.pieces}))
+    fn = RMSNorm(W, 1e-5)
+    bindings.append(Binding(fn, {"weight": "fn"}))
+    head = OutputHead(V, W, tied_to=embed)
+
+    class Cfg:
+        architecture = "ToyRoutedForTest"
+        max_position_embeddings = 256
+    model = DecoderModel(Cfg(), embed, blocks, [LayerCall(0, 0), LayerCall(1, 1)], fn, head, bindings)
+    g = torch.Generator().manual_seed(11)
+    tensors = {}
+    for b in bindings:
+        for p in b.part.params():
+            for pc in p.pieces:
+                t = torch.randn(pc.shape, generator=g) * 0.3
+                tensors[b.names[pc.key]] = t + 1 if p.init == "one_plus_normal" else t
+    ecfg = EngineConfig(dtype="float32", page_size=4, max_cache_tokens=256, max_num_seqs=3, use_cuda_graph=False,
+                        device=DEV)
+    load_state_dict(model, tensors, torch.float32, DEV)
+    model.materialize(DEV, torch.float32)
+    runner = ModelRunner(model, make_cache(model, ecfg), ecfg)
+
+    def attention(h, l, nh, nkv, theta, slowdown, window):
+        T = h.shape[0]
+        w = {k[len(f"l{l}.mixer."):]: v for k, v in tensors.items() if k.startswith(f"l{l}.mixer.")}
+        q = (h @ w["q.weight"].T + w["q.bias"]).view(T, nh, hd)
+        k = (h @ w["k.weight"].T + w["k.bias"]).view(T, nkv, hd)
+        v = (h @ w["v.weight"].T + w["v.bias"]).view(T, nkv, hd)
+        pos = torch.arange(T)
+        cos, sin = plain.rotary_angles(pos.float() / slowdown, hd, theta)
+        o = plain.attention_scores_softmax_pv(plain.apply_rotary(q, cos, sin), plain.apply_rotary(k, cos, sin), v, pos,
+                                              window)
+        return o.reshape(T, nh * hd) @ w["o.weight"].T
+
+    routed = []
+
+    def reference(ids):
+        x = plain.embed(torch.tensor(ids), tensors["emb"])
+        x = x + attention(plain.rms_norm(x, tensors["l0.norm1.weight"], 1e-5), 0, 3, 1, 300.0, 3.0, None)
+        h = plain.rms_norm(x, tensors["l0.norm2.weight"], 1e-5)
+        choice = (h @ tensors["l0.feed_forward.router"].T).argmax(-1)
+        routed.append(choice)
+        y = torch.zeros_like(h)
+        for t in range(h.shape[0]):
+            e = int(choice[t])
+            w = {f"{n}_proj.weight": tensors[f"l0.feed_forward.e{e}.{n}"] for n in ("gate", "up", "down")}
+            y[t] = plain.swiglu_mlp(h[t:t + 1], w, "")[0]
+        x = x + y
+        x = x + attention(plain.rms_norm(x, tensors["l1.norm1.weight"], 1e-6), 1, 2, 2, 5000.0, 1.0, 9)
+        w = {f"{n}_proj.weight": tensors[f"l1.feed_forward.{n}.weight"] for n in ("gate", "up", "down")}
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, tensors["l1.norm2.weight"], 1e-6), w, "")
+        return plain.rms_norm(x, tensors["fn"], 1e-5) @ tensors["emb"].T
+
+    ids = {"p": helpers.random_ids(31, V, 7), "q": helpers.random_ids(18, V, 8), "r": helpers.random_ids(9, V, 9)}
+    ref = {rid: reference(t) for rid, t in ids.items()}
+    assert len(set(torch.cat(routed).tolist())) == E, "the test should reach every expert"
+    for steps in (helpers.trace_whole(ids), helpers.trace_mixed(ids, max_live=3, seed=5, chunk_sizes=(4, 2, 7))):
+        want = helpers.expected_logits(steps, ids, ref)
+        for i, (gg, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+            if w is not None:
+                helpers.assert_close_logits(gg, w, 5e-5, f"toy routed step {i}")
+    assert all(gr.pool.in_use == 0 for gr in runner.cache.groups)
