@@ -34,6 +34,9 @@ class EngineConfig:
     max_model_len: Optional[int] = None  # longest request; None = max_position_embeddings
     use_cuda_graph: bool = True        # replay decode-only steps from a CUDA graph (pico_vllm/engine.py:98-137)
     graph_batch_sizes: Tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64)
+    # a step that is one full portion of one prompt is replayed from a graph too (long prompts come as a row of
+    # such steps): its number of tokens; None = the longest portion (prefill_chunk or the budget), 0 = never
+    graph_prefill_tokens: Optional[int] = None
     async_scheduling: bool = True      # launch a step before the tokens of the step before are read
     seed: int = 0
     device: str = "cuda:0"

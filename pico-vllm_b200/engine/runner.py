@@ -7,7 +7,9 @@ and commits the tokens to the cache.  Portions of prompts and single decoded tok
 batch; nothing but the given tokens is computed.  Steps that hold only single tokens are
 replayed from a CUDA graph per batch-size bucket (the reference captures one graph at a fixed
 batch of 8 and pads with ghost rows, pico_vllm/engine.py:98-191); padding rows have position
--1, which every kernel treats as "no keys, no store".
+-1, which every kernel treats as "no keys, no store".  A step that is one full portion of one
+prompt (``EngineConfig.graph_prefill_tokens``) is recorded and replayed in the same way: long
+prompts arrive as a row of such steps, and a replay saves the gaps between their ~250 launches.
 
 Counterpart of the tensor building in pico_vllm/engine.py:146-181, 199-220, 325-342, which
 runs one forward per prompt plus one for all decoding requests.
@@ -83,7 +85,11 @@ class ModelRunner:
         self.device = cache.device
         self.on_gpu = self.device.type == "cuda"
         self.views = cache.views()
-        self._graphs: Dict[int, dict] = {}
+        self._graphs: dict = {}          # decode bucket, or ("prefill", tokens, wanted rows) -> recorded step
+        g = cfg.graph_prefill_tokens
+        if g is None:
+            g = min(cfg.prefill_chunk or cfg.max_num_batched_tokens, cfg.max_num_batched_tokens)
+        self._graph_prefill_tokens = g if g > 1 else -1
         self._scratch: Optional[torch.Tensor] = None
         self._stage: Optional[_Staging] = None
         self.graph_replays = 0
@@ -137,17 +143,29 @@ class ModelRunner:
             return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
         V = self.model.vocab_size
         seen = set()
+        checked = []
         for it in items:
             if len(it.tokens) < 1:
                 raise PicoError("a step item needs at least one token")
             if it.slot in seen:
                 raise PicoError(f"slot {it.slot} appears twice in one step")
             seen.add(it.slot)
-            if min(it.tokens) < -self.feedback.shape[0] or max(it.tokens) >= V:
+            toks = it.tokens
+            if len(toks) > 32 and not isinstance(toks, np.ndarray):
+                # a portion of a prompt: one conversion serves the check here and the copy in _build
+                try:
+                    toks = np.asarray(toks, dtype=np.int32)
+                except (OverflowError, ValueError, TypeError):
+                    raise PicoError(f"token id outside [0, {V}) in a step item") from None
+                it = StepItem(it.slot, toks, it.want)
+            lo, hi = (int(toks.min()), int(toks.max())) if isinstance(toks, np.ndarray) else (min(toks), max(toks))
+            if lo < -self.feedback.shape[0] or hi >= V:
                 raise PicoError(f"token id outside [0, {V}) in a step item")
             for w in it.want:
                 if not 0 <= w < len(it.tokens):
                     raise PicoError(f"wanted place {w} outside the {len(it.tokens)} tokens given")
+            checked.append(it)
+        items = checked
         starts = []
         done = []
         try:
@@ -163,6 +181,9 @@ class ModelRunner:
             if (decode_only and self.cfg.use_cuda_graph and self.on_gpu
                     and len(items) <= max(self.cfg.graph_batch_sizes)):
                 logits = self._step_graph(items, starts)
+            elif (len(items) == 1 and len(items[0].tokens) == self._graph_prefill_tokens and len(items[0].want) <= 1
+                    and self.cfg.use_cuda_graph and self.on_gpu):
+                logits = self._step_prefill_graph(items, starts)
             else:
                 batch = self._build(items, starts, pad_to=None)
                 logits = self.model.forward(batch, self.views)
@@ -176,7 +197,7 @@ class ModelRunner:
         return logits
 
     def _build(self, items: Sequence[StepItem], starts: List[int], pad_to: Optional[int],
-               splits: Optional[int] = None, buffers=None, scratch=None) -> Batch:
+               splits: Optional[int] = None, buffers=None, scratch=None, rows: Optional[int] = None) -> Batch:
         """Index arrays of the step on the device.  ``pad_to``: number of one-token segments of
         a graph bucket (the batch is padded to it and the block tables keep their full width);
         ``buffers``/``scratch``: the bucket's own staging and scratch tensors, which must not move."""
@@ -192,7 +213,8 @@ class ModelRunner:
             want_rows.extend(at + w for w in it.want)
             at += n
         R_real = len(want_rows)
-        R = R_real if pad_to is None else S     # a graph's shape is fixed: one row per segment
+        # a graph's shape is fixed: one row per segment, or the number the caller fixes
+        R = R_real if pad_to is None else (S if rows is None else rows)
         if pad_to is not None and R_real > R:
             raise PicoError("more logits wanted than the graph holds")
         kv_lens = [st + n for st, n in zip(starts, q_lens)]
@@ -287,6 +309,33 @@ class ModelRunner:
         if len(rows) == len(items):
             return logits[:len(items)]
         return logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else logits[:0]
+
+    def _step_prefill_graph(self, items: Sequence[StepItem], starts: List[int]) -> torch.Tensor:
+        """One full portion of one prompt: the same work every time but for the index arrays, so it is
+        recorded once (per number of wanted rows, 0 or 1) and replayed over its own staging buffers."""
+        T, R = len(items[0].tokens), len(items[0].want)
+        key = ("prefill", T, R)
+        entry = self._graphs.get(key)
+        if entry is None:
+            lay = _Layout(T, 1, R, len(self.cache.groups), self.cache.max_blocks)
+            buffers = _Staging(lay.total, self.device)
+            batch = self._build(items, starts, pad_to=1, splits=1, buffers=buffers, scratch=None, rows=R)
+            self.model.forward(batch, self.views)       # eager warm-up; writes the same cache rows
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(batch, self.views)
+            entry = {"graph": graph, "logits": logits, "launches": ops.launches - before, "batch": batch,
+                     "buffers": buffers}
+            self._graphs[key] = entry
+            graph.replay()
+        else:
+            self._build(items, starts, pad_to=1, splits=1, buffers=entry["buffers"], scratch=None, rows=R)
+            entry["graph"].replay()
+            ops._count(entry["launches"])
+        self.graph_replays += 1
+        return entry["logits"]
 
     def _capture(self, B: int, items: Sequence[StepItem], starts: List[int]) -> dict:
         """First decode step at this bucket: run it once eagerly (this also warms up the
