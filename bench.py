@@ -341,6 +341,23 @@ def run_micro(args):
                                                         ps, None, hd ** -0.5, 1, None, *maps)] * 8)
         fl = 2.0 * 2 * nh * hd * M * (M + 1) / 2          # the visible (query, key) pairs only
         out["prefill_attention"] = {"us": round(t, 1), "tflops_causal": round(fl / t / 1e6)}
+        if M <= 4096:
+            # the same M tokens as a portion after 14,336 others: with two blocks per query tile, and with one
+            ctx = 14336
+            blocks = (ctx + M + ps - 1) // ps
+            k = torch.randn(blocks, nkv, ps, hd, device=dev).bfloat16()
+            v = torch.randn(blocks, nkv, ps, hd, device=dev).bfloat16()
+            table = torch.randperm(blocks, device=dev).int().view(1, blocks).contiguous()
+            pos = torch.arange(ctx, ctx + M, device=dev).int()
+            maps = (ops.make_kv_tensor_map(k), ops.make_kv_tensor_map(v), ops.make_kv_tensor_map_2d(k),
+                    ops.make_kv_tensor_map_2d(v, values=True))
+            scratch = torch.empty(ops.attention_scratch_floats(M, nh, hd, 2), dtype=torch.float32, device=dev)
+            t1 = graph_time([lambda: ops.paged_attention_mma(q, k, v, o, seg, pos, table, cu, pf, 1, M, dec, 0, nh, nkv,
+                                                             hd, ps, None, hd ** -0.5, 1, None, *maps)] * 4)
+            t2 = graph_time([lambda: ops.paged_attention_mma(q, k, v, o, seg, pos, table, cu, pf, 1, M, dec, 0, nh, nkv,
+                                                             hd, ps, None, hd ** -0.5, 1, scratch, *maps,
+                                                             pair_min_keys=6144)] * 4)
+            out["prefill_attention_after_14336"] = {"us": round(t2, 1), "one_block_per_tile_us": round(t1, 1)}
         print(json.dumps(out))
         return 0
     nh, nkv, hd, ps, L, ctx = 12, 2, 128, 16, 24, args.context

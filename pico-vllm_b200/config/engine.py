@@ -37,6 +37,9 @@ class EngineConfig:
     # a step that is one full portion of one prompt is replayed from a graph too (long prompts come as a row of
     # such steps): its number of tokens; None = the longest portion (prefill_chunk or the budget), 0 = never
     graph_prefill_tokens: Optional[int] = None
+    # portions of prompts whose requests already hold at least this many tokens get two blocks per query tile in
+    # attention, half of the keys each (a few long tiles would otherwise set the kernel's time); 0 = never
+    pair_min_context: int = 6144
     async_scheduling: bool = True      # launch a step before the tokens of the step before are read
     seed: int = 0
     device: str = "cuda:0"

@@ -179,7 +179,9 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                              const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out,
                              const int* __restrict__ seg_list, const int* __restrict__ cu_q,
                              const int* __restrict__ positions, const int* __restrict__ block_table, int table_stride,
-                             int nh, int nkv, int page_size, int window, float scale_log2) {
+                             int nh, int nkv, int page_size, int window, float scale_log2,
+                             float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                             size_t n_rows, int n_parts, int split_min) {
     pdl_launch_dependents();
     extern __shared__ unsigned char tca_dyn[];
     constexpr int NH = HD / 64;                              // 64-dim blocks of a head
@@ -232,13 +234,25 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const int seg = seg_list ? seg_list[blockIdx.z] : blockIdx.z;
     const int q0 = cu_q[seg], qlen = cu_q[seg + 1] - q0;
     // the tiles with the most keys (the last tokens) are launched first, so that they do not form the tail
-    const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * tpt;
-    const bool active = tok0 < qlen;                         // uniform for the block
-    const int ntok = active ? min(tpt, qlen - tok0) : 0;
-    const int pos0 = active ? positions[q0] + tok0 : 0;      // position of the tile's first token
+    // With n_parts = 2 a query tile has two blocks, neighbours in the grid: when the tile sees split_min key
+    // tiles or more, each takes half of them and the one that finishes last adds the two partial results;
+    // otherwise the first block takes all and the second has nothing to do.
+    const int n_qt = (int)gridDim.x / n_parts;
+    const int qt = (int)blockIdx.x / n_parts, part = (int)blockIdx.x - qt * n_parts;
+    const int tok0 = (n_qt - 1 - qt) * tpt;
+    const bool tile_ok = tok0 < qlen;                        // uniform for the block
+    const int ntok = tile_ok ? min(tpt, qlen - tok0) : 0;
+    const int pos0 = tile_ok ? positions[q0] + tok0 : 0;     // position of the tile's first token
     const int hi = pos0 + ntok;                              // one past the last visible key of the tile
     const int lo = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
-    const int t_begin = lo / TCA_BN, t_end = active ? (hi + TCA_BN - 1) / TCA_BN : 0;
+    int t_begin = lo / TCA_BN, t_end = tile_ok ? (hi + TCA_BN - 1) / TCA_BN : 0;
+    const bool split = n_parts == 2 && tile_ok && t_end - t_begin >= split_min;
+    if (split) {
+        const int half = (t_end - t_begin + 1) / 2;
+        if (part == 0) t_end = t_begin + half;
+        else t_begin += half;
+    }
+    const bool active = tile_ok && (part == 0 || split);
     const int ntiles = active ? t_end - t_begin : 0;
     const int* table = block_table + (size_t)seg * table_stride;
     const int ppt = TCA_BN / page_size;
@@ -496,10 +510,12 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
             *abort_s = 1;
         }
         ml_s[pipe * TCA_BM + r] = make_float2(m_use, l);
+        // one thread's view of the error flag, so that all 256 take the same way through the barriers below
+        if (r == 0 && pipe == 0) const_cast<int*>(abort_s)[2] = *abort_s;
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        tca_softmax_sync();              // every softmax thread comes here exactly once
+        tca_softmax_sync();              // every softmax thread comes here
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        if (ntiles > 0 && !*abort_s) {
+        if (ntiles > 0 && !abort_s[2]) {
             // out = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)); each pipeline's
             // warps write half of the head's dims.  A pipeline without tiles holds nothing that may be read.
             const bool two = ntiles > 1;
@@ -507,10 +523,72 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
             const float m = fmaxf(a.x, b.x);
             const float fa = a.x == -INFINITY ? 0.f : tca_exp2(a.x - m), fb = b.x == -INFINITY ? 0.f : tca_exp2(b.x - m);
             const float den = a.y * fa + b.y * fb;
-            const float inv = den > 0.f ? 1.0f / den : 0.f;
-            const float wa = fa * inv, wb = fb * inv;
             const uint32_t o_a = tmem_base + TCA_COL_O + lane_off, o_b = o_a + HD;
-            bf16* dst = out + ((size_t)(q0 + tok0 + (row_ok ? tok : 0)) * nh + kh * g + head) * HD;
+            const size_t orow = (size_t)(q0 + tok0 + (row_ok ? tok : 0)) * nh + kh * g + head;
+            bf16* dst = out + orow * HD;
+            float wa = fa, wb = fb, w_other = 0.f;            // weights of this block's two sums and of the other block's
+            const float* other_o = nullptr;
+            bool write_out = true;
+            if (split) {
+                // this block's sum, not yet divided, and its maximum and denominator go to scratch; the block of
+                // the pair that gets there last reads the other's and writes the result.  The sum below is the same
+                // whichever of the two comes last.
+                float* my_o = part_o + ((size_t)part * n_rows + orow) * HD;
+#pragma unroll 1
+                for (int c = pipe * (HD / 2); c < (pipe + 1) * (HD / 2); c += 32) {
+                    uint32_t ov[32], ow[32];
+                    tca_ld32(o_a + c, ov);
+                    if (two) tca_ld32(o_b + c, ow);          // a pipeline without tiles holds nothing that may be read
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 y;
+                            y.x = __uint_as_float(ov[i]) * fa;
+                            y.y = __uint_as_float(ov[i + 1]) * fa;
+                            y.z = __uint_as_float(ov[i + 2]) * fa;
+                            y.w = __uint_as_float(ov[i + 3]) * fa;
+                            if (two) {
+                                y.x += __uint_as_float(ow[i]) * fb;
+                                y.y += __uint_as_float(ow[i + 1]) * fb;
+                                y.z += __uint_as_float(ow[i + 2]) * fb;
+                                y.w += __uint_as_float(ow[i + 3]) * fb;
+                            }
+                            *reinterpret_cast<float4*>(my_o + c + i) = y;
+                        }
+                    }
+                }
+                if (pipe == 0 && row_ok)
+                    *reinterpret_cast<float2*>(part_ml + ((size_t)part * n_rows + orow) * 2) = make_float2(m, den);
+                __threadfence();
+                tca_softmax_sync();
+                if (r == 0 && pipe == 0) {
+                    int* cnt = counters + ((size_t)blockIdx.z * nkv + kh) * n_qt + qt;
+                    const int before = atomicAdd(cnt, 1);
+                    if (before == 1) *cnt = 0;                 // both have arrived: ready for the next launch
+                    const_cast<int*>(abort_s)[1] = before;
+                }
+                tca_softmax_sync();
+                write_out = abort_s[1] == 1;
+                if (write_out) {
+                    __threadfence();
+                    other_o = part_o + ((size_t)(1 - part) * n_rows + orow) * HD;
+                    const float2 o_ml = row_ok ? __ldcg(reinterpret_cast<const float2*>(part_ml + ((size_t)(1 - part) * n_rows + orow) * 2))
+                                               : make_float2(-INFINITY, 0.f);
+                    const float mm = fmaxf(m, o_ml.x);
+                    const float f1 = m == -INFINITY ? 0.f : tca_exp2(m - mm), f2 = o_ml.x == -INFINITY ? 0.f : tca_exp2(o_ml.x - mm);
+                    const float dd = den * f1 + o_ml.y * f2;
+                    const float inv2 = dd > 0.f ? 1.0f / dd : 0.f;
+                    wa = fa * f1 * inv2;
+                    wb = fb * f1 * inv2;
+                    w_other = f2 * inv2;
+                }
+            } else {
+                const float inv = den > 0.f ? 1.0f / den : 0.f;
+                wa = fa * inv;
+                wb = fb * inv;
+            }
+            if (write_out) {
 #pragma unroll 1
             for (int c = pipe * (HD / 2); c < (pipe + 1) * (HD / 2); c += 32) {
                 uint32_t ov[32], ow[32];
@@ -529,12 +607,18 @@ paged_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                                 y0 += __uint_as_float(ow[i + e]) * wb;
                                 y1 += __uint_as_float(ow[i + e + 1]) * wb;
                             }
+                            if (other_o) {
+                                const float2 t2 = __ldcg(reinterpret_cast<const float2*>(other_o + c + i + e));
+                                y0 += t2.x * w_other;
+                                y1 += t2.y * w_other;
+                            }
                             __nv_bfloat162 h2 = __floats2bfloat162_rn(y0, y1);
                             o32[e / 2] = *reinterpret_cast<uint32_t*>(&h2);
                         }
                         *reinterpret_cast<uint4*>(dst + c + i) = o4;
                     }
                 }
+            }
             }
         }
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -592,10 +676,17 @@ PICO_API int pico_make_kv_tensor_map_2d(void* map_out, const void* base, long lo
 }
 
 // Prompt portions on tcgen05; arguments as pico_paged_prefill_mma, with the 2-D tensor maps above.
+// pair_min_keys > 0: every query tile gets two blocks, and a tile that sees at least that many keys is shared by
+// them.  This pays when a few long tiles would otherwise set the kernel's time (a portion late in a long context:
+// 286 instead of 331 us for 2,048 tokens after 14,336); a pair costs ~10 us for its second prologue, the partial
+// results through scratch and their sum, so short tiles lose (2,048 tokens from the start: 57 instead of 30 us when
+// tiles from 512 keys on are shared).  scratch: float32 [2][n_tokens][nh][hd + 2]; counters: n_counters int32,
+// zero before the first launch (the kernel leaves them zero).
 PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, const void* q, int q_row_stride, void* out,
                                         const int* seg_list, int n_segs, const int* cu_q, int max_q_len,
                                         const int* positions, const int* block_table, int table_stride, int nh, int nkv,
-                                        int hd, int page_size, int window, float scale, cudaStream_t stream) {
+                                        int hd, int page_size, int window, float scale, int pair_min_keys, float* scratch,
+                                        int n_tokens, int* counters, int n_counters, cudaStream_t stream) {
     if (n_segs <= 0 || max_q_len <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0) return PICO_ERR_SIZE;
     const int g = nh / nkv;
@@ -603,7 +694,13 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
     if (page_size < 8 || TCA_BN % page_size != 0) return PICO_ERR_SIZE;
     if (q_row_stride % 8 != 0) return PICO_ERR_ALIGN;
     const int tpt = TCA_BM / g;
-    const dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_segs);
+    const int n_qt = (max_q_len + tpt - 1) / tpt;
+    const int n_parts = (pair_min_keys > 0 && scratch && counters && (long long)n_qt * nkv * n_segs <= n_counters && n_tokens > 0) ? 2 : 1;
+    const size_t n_rows = (size_t)n_tokens * nh;
+    const int split_min = pair_min_keys / TCA_BN > 2 ? pair_min_keys / TCA_BN : 2;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + 2 * n_rows * hd : nullptr;
+    const dim3 grid(n_qt * n_parts, nkv, n_segs);
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = (size_t)TCA_STAGES * 2 * TCA_BN * hd * 2 + (4 * TCA_STAGES + 9) * 8 + 16 + 2 * TCA_BM * 8 + TCA_TABLE_CACHE * 4 + 1024;
     CUtensorMap km, vm;
@@ -614,7 +711,7 @@ PICO_API int pico_paged_prefill_tcgen05(const void* k_map, const void* v_map, co
         cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         pico_launch((paged_prefill_tcgen05_kernel<HD>), grid, dim3(TCA_THREADS), smem, stream, km, vm, (const bf16*)q,   \
                     q_row_stride, (bf16*)out, seg_list, cu_q, positions, block_table, table_stride, nh, nkv, page_size,  \
-                    window, scale_log2);                                                                                 \
+                    window, scale_log2, part_o, part_ml, counters, n_rows, n_parts, split_min);                          \
     } while (0)
     if (hd == 64) LAUNCH_TCA(64);
     else LAUNCH_TCA(128);

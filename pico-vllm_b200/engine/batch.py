@@ -36,6 +36,8 @@ class Batch:
     kv_lens: List[int]           # host copy: length of each segment's request after this step
     attn_splits: int = 1         # parts each token's key range is cut into
     scratch: Optional[torch.Tensor] = None   # float32 scratch for split attention
+    pair_min_keys: int = 0       # > 0: prompt attention gives every query tile two blocks, which share a tile that sees
+                                 # at least this many keys (the scratch then holds two partial results per token and head)
     decode_only: bool = False
     # the batch split for kernels that treat portions and single tokens differently
     prefill_segs: Optional[torch.Tensor] = None   # int32: segments with two or more tokens (None: all)

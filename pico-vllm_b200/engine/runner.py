@@ -104,6 +104,9 @@ class ModelRunner:
             if hasattr(m, "n_heads"):
                 self._max_heads = max(self._max_heads, m.n_heads * (m.head_dim + 2))
         self._min_kv_heads = min((s.n_kv_heads for s in kv), default=1)
+        # query heads of a layer: what one token adds to the 128-row query tiles of prompt attention
+        self._tile_load = max((blk.mixer.n_heads for blk in model.blocks if hasattr(blk.mixer, "n_heads")), default=1)
+        self._num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.on_gpu else 1
 
     # ------------------------------------------------------------------ buffers
     def _staging(self, n: int) -> _Staging:
@@ -126,7 +129,21 @@ class ModelRunner:
             splits *= 2
         return splits
 
-    def _scratch_for(self, T: int, splits: int) -> Optional[torch.Tensor]:
+    def _pair_min_keys(self, q_lens: List[int], starts: List[int]) -> int:
+        """Whether prompt attention should give every query tile two blocks (the threshold in keys, or 0): only
+        when every portion of the step comes after a long context, where a tile takes long enough to pay for the
+        pair, and when the tiles are too few to keep the SMs busy by themselves (under two per SM)."""
+        m = self.cfg.pair_min_context
+        if not (m > 0 and q_lens and self.on_gpu and self.cfg.dtype == "bfloat16" and min(starts) >= m):
+            return 0
+        tiles = len(q_lens) * self._tile_load * -(-max(q_lens) // 128)
+        return m if tiles <= 2 * self._num_sms else 0
+
+    def _scratch_for(self, T: int, splits: int, pairs: bool = False) -> Optional[torch.Tensor]:
+        """Float32 scratch of the attention kernels: partial results of the parts of a single token's key
+        range, and two per (token, head) for query tiles of prompts that two blocks share."""
+        if pairs:
+            splits = max(splits, 2)
         if splits <= 1:
             return None
         need = T * splits * self._max_heads
@@ -197,7 +214,8 @@ class ModelRunner:
         return logits
 
     def _build(self, items: Sequence[StepItem], starts: List[int], pad_to: Optional[int],
-               splits: Optional[int] = None, buffers=None, scratch=None, rows: Optional[int] = None) -> Batch:
+               splits: Optional[int] = None, buffers=None, scratch=None, rows: Optional[int] = None,
+               pair: Optional[int] = None) -> Batch:
         """Index arrays of the step on the device.  ``pad_to``: number of one-token segments of
         a graph bucket (the batch is padded to it and the block tables keep their full width);
         ``buffers``/``scratch``: the bucket's own staging and scratch tensors, which must not move."""
@@ -276,11 +294,13 @@ class ModelRunner:
         max_kv = max(kv_lens)
         if splits is None:
             splits = self._splits(T, max_kv)
+        pair_min = self._pair_min_keys([q_lens[i] for i in pf], [starts[i] for i in pf]) if pair is None else pair
         return Batch(num_tokens=T, num_segments=S, token_ids=d(lay.token_ids, T), positions=d(lay.positions, T),
                      tok_seg=d(lay.tok_seg, T), seg_slots=d(lay.seg_slots, S), cu_q=d(lay.cu_q, S + 1),
                      logit_rows=d(lay.logit_rows, R), num_logit_rows=R, groups=groups, q_lens=q_lens,
                      kv_lens=kv_lens, attn_splits=splits,
-                     scratch=scratch if scratch is not None else self._scratch_for(T, splits),
+                     scratch=scratch if scratch is not None else self._scratch_for(T, splits, pair_min > 0),
+                     pair_min_keys=pair_min,
                      decode_only=all(n == 1 for n in q_lens),
                      prefill_segs=d(lay.prefill_segs, len(pf)) if len(pf) < S else None, num_prefill_segs=len(pf),
                      max_prefill_q=max([q_lens[i] for i in pf], default=0),
@@ -314,12 +334,15 @@ class ModelRunner:
         """One full portion of one prompt: the same work every time but for the index arrays, so it is
         recorded once (per number of wanted rows, 0 or 1) and replayed over its own staging buffers."""
         T, R = len(items[0].tokens), len(items[0].want)
-        key = ("prefill", T, R)
+        pair = self._pair_min_keys([T], starts)
+        key = ("prefill", T, R, pair)
         entry = self._graphs.get(key)
         if entry is None:
             lay = _Layout(T, 1, R, len(self.cache.groups), self.cache.max_blocks)
             buffers = _Staging(lay.total, self.device)
-            batch = self._build(items, starts, pad_to=1, splits=1, buffers=buffers, scratch=None, rows=R)
+            # a graph keeps the addresses it was recorded with: staging and attention scratch are its own
+            scratch = torch.empty(2 * T * self._max_heads, dtype=torch.float32, device=self.device) if pair else None
+            batch = self._build(items, starts, pad_to=1, splits=1, buffers=buffers, scratch=scratch, rows=R, pair=pair)
             self.model.forward(batch, self.views)       # eager warm-up; writes the same cache rows
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
@@ -327,11 +350,12 @@ class ModelRunner:
             with torch.cuda.graph(graph):
                 logits = self.model.forward(batch, self.views)
             entry = {"graph": graph, "logits": logits, "launches": ops.launches - before, "batch": batch,
-                     "buffers": buffers}
+                     "buffers": buffers, "scratch": scratch}
             self._graphs[key] = entry
             graph.replay()
         else:
-            self._build(items, starts, pad_to=1, splits=1, buffers=entry["buffers"], scratch=None, rows=R)
+            self._build(items, starts, pad_to=1, splits=1, buffers=entry["buffers"], scratch=entry["scratch"], rows=R,
+                        pair=pair)
             entry["graph"].replay()
             ops._count(entry["launches"])
         self.graph_replays += 1

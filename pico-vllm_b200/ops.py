@@ -66,7 +66,8 @@ def library():
                                   f32, i32, vp],
         "pico_tma_status": [vp],
         "pico_make_kv_tensor_map_2d": [vp, vp, i64, i32, i32, i32],
-        "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp],
+        "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32,
+                                       vp, i32, vp, i32, vp],
         "pico_tca_status": [vp],
         "pico_gemm_tcgen05": [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp],
         "pico_tc_status": [vp],
@@ -309,13 +310,27 @@ def tma_status() -> int:
     return out.value
 
 
+_PAIR_COUNTERS = {}
+
+
+def _pair_counters(device: torch.device):
+    """Zeroed int32 counters for the pairs of blocks that share a query tile in prompt attention (one per
+    device; the kernel leaves them zero).  None while a graph is being recorded before they exist."""
+    c = _PAIR_COUNTERS.get(device)
+    if c is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        c = _PAIR_COUNTERS[device] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+    return c
+
+
 def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
                         tok_seg: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                         cu_q: torch.Tensor, prefill_segs: Optional[torch.Tensor], n_prefill_segs: int,
                         max_prefill_q: int, decode_tokens: Optional[torch.Tensor], n_decode_tokens: int,
                         n_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
                         scale: float, n_splits: int = 1, scratch: Optional[torch.Tensor] = None,
-                        k_map=None, v_map=None, k_map2d=None, v_map2d=None) -> torch.Tensor:
+                        k_map=None, v_map=None, k_map2d=None, v_map2d=None, pair_min_keys: int = 0) -> torch.Tensor:
     """The same attention as :func:`paged_attention` for bfloat16 on tensor cores, in two launches:
     segments that bring two or more tokens (``prefill_segs`` int32 [n_prefill_segs], None = all
     segments; ``cu_q`` int32 [segments + 1]; ``max_prefill_q`` their longest) and single tokens
@@ -343,10 +358,19 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     lib = library()
     win = int(window) if window else 0
     if n_prefill_segs > 0 and k_map2d is not None and v_map2d is not None:
+        # pair_min_keys > 0 (and scratch for two partial results per (token, head)): every query tile gets two
+        # blocks, which share it when it sees at least that many keys; the pairs' counters are zero between launches
+        T = q.shape[0]
+        counters = _pair_counters(q.device) if pair_min_keys > 0 else None
+        split = (counters is not None and scratch is not None and scratch.dtype == torch.float32
+                 and scratch.numel() >= 2 * T * n_heads * (head_dim + 2))
         _check(lib.pico_paged_prefill_tcgen05(k_map2d[1], v_map2d[1], _ptr(q), q.stride(0), _ptr(out),
                                               _ptr(prefill_segs), n_prefill_segs, _ptr(cu_q), max_prefill_q,
                                               _ptr(positions), _ptr(block_table), block_table.stride(0), n_heads,
-                                              n_kv_heads, head_dim, page_size, win, float(scale), _stream()),
+                                              n_kv_heads, head_dim, page_size, win, float(scale),
+                                              int(pair_min_keys) if split else 0, _ptr(scratch) if split else None, T,
+                                              _ptr(counters) if split else None, counters.numel() if split else 0,
+                                              _stream()),
                f"paged_prefill_tcgen05 (head_dim {head_dim})")
         _count()
     elif n_prefill_segs > 0:

@@ -79,7 +79,8 @@ class GQAAttention(Part):
                                     batch.cu_q, batch.prefill_segs, batch.num_prefill_segs, batch.max_prefill_q,
                                     batch.decode_tokens, batch.num_decode_tokens, self.n_heads, self.n_kv_heads,
                                     self.head_dim, cache.page_size, self.window, self.scale, batch.attn_splits,
-                                    batch.scratch, cache.k_map, cache.v_map, cache.k_map2d, cache.v_map2d)
+                                    batch.scratch, cache.k_map, cache.v_map, cache.k_map2d, cache.v_map2d,
+                                    batch.pair_min_keys)
         else:       # float32, or sizes the tensor-core kernels do not take
             ops.paged_attention(qkv, cache.k, cache.v, out, batch.tok_seg, batch.positions, gb.block_table,
                                 self.n_heads, self.n_kv_heads, self.head_dim, cache.page_size, self.window,

@@ -105,7 +105,7 @@ def mma_attention_takes(dtype, n_heads, n_kv_heads, head_dim):
 def paged_attention_mma(q, k_pages, v_pages, out, tok_seg, positions, block_table, cu_q, prefill_segs,
                         n_prefill_segs, max_prefill_q, decode_tokens, n_decode_tokens, n_heads, n_kv_heads, head_dim,
                         page_size, window, scale, n_splits=1, scratch=None, k_map=None, v_map=None, k_map2d=None,
-                        v_map2d=None):
+                        v_map2d=None, pair_min_keys=0):
     return paged_attention(q, k_pages, v_pages, out, tok_seg, positions, block_table, n_heads, n_kv_heads, head_dim,
                            page_size, window, scale)
 

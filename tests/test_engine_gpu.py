@@ -467,18 +467,19 @@ def test_full_portions_are_replayed_from_a_graph(dtype, name):
     """A step that is one portion of one prompt with the configured number of tokens is recorded once
     and replayed: here portions of 24 tokens of three requests, at changing places of their prompts, with
     no row, the last row or another row wanted, between steps of other shapes and with pages that come
-    back from ended requests."""
+    back from ended requests.  Portions that come after 40 tokens or more also get two blocks per query tile in
+    the tensor-core attention kernel (configuration d in bfloat16), recorded and launched directly."""
     from pico_vllm_b200.config import EngineConfig
     from pico_vllm_b200.engine import ModelRunner, make_cache, model_from_tensors
     cfg = helpers.tiny_config(name)
     P = 24
-    ecfg = EngineConfig(dtype=dtype, page_size=helpers.TINY[name]["page_size"], max_cache_tokens=192, max_num_seqs=2,
-                        use_cuda_graph=True, graph_prefill_tokens=P, device=DEV)
+    ecfg = EngineConfig(dtype=dtype, page_size=helpers.TINY[name]["page_size"], max_cache_tokens=224, max_num_seqs=2,
+                        use_cuda_graph=True, graph_prefill_tokens=P, pair_min_context=40, device=DEV)
     tensors = helpers.tiny_tensors(name, torch.float32 if dtype == "float32" else torch.bfloat16)
     model = model_from_tensors(cfg, tensors, ecfg)
     runner = ModelRunner(model, make_cache(model, ecfg, poison_freed=True), ecfg)
     reqs = {"x": helpers.random_ids(3 * P + 5, cfg.vocab_size, 41), "y": helpers.random_ids(2 * P, cfg.vocab_size, 42),
-            "z": helpers.random_ids(P + 30, cfg.vocab_size, 43)}
+            "z": helpers.random_ids(P + 30 + 47, cfg.vocab_size, 43)}
     x, y, z = reqs["x"], reqs["y"], reqs["z"]
     steps = [dict(entries=[dict(id="x", tokens=x[:P], want=[])], end=[]),                       # recorded, no row
              dict(entries=[dict(id="y", tokens=y[:P], want=[P - 1])], end=[]),                   # recorded, one row
@@ -486,7 +487,8 @@ def test_full_portions_are_replayed_from_a_graph(dtype, name):
              dict(entries=[dict(id="x", tokens=x[2 * P:3 * P], want=[])], end=[]),               # replayed
              dict(entries=[dict(id="x", tokens=x[3 * P:], want=[4]), dict(id="y", tokens=y[P:P + 3], want=[2])], end=["x"]),
              dict(entries=[dict(id="z", tokens=z[:30], want=[29])], end=[]),                     # other shape, x's pages
-             dict(entries=[dict(id="z", tokens=z[30:], want=[P - 1])], end=["z"]),               # replayed, late place
+             dict(entries=[dict(id="z", tokens=z[30:30 + P], want=[P - 1])], end=[]),            # replayed, late place
+             dict(entries=[dict(id="z", tokens=z[30 + P:], want=[0, 46])], end=["z"]),           # after 54 tokens, launched directly
              dict(entries=[dict(id="y", tokens=y[P + 3:], want=[P - 4])], end=["y"])]
     want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
     got = helpers.replay(runner, steps)

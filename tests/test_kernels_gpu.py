@@ -100,7 +100,7 @@ def test_rope_store(dtype, nh, nkv, hd, ps, rot):
 
 
 def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, seed=0, spike=False, mma=False,
-                    tma=False, poison=False, tc=False):
+                    tma=False, poison=False, tc=False, pair=False):
     """Segments with kv lengths seg_lens, of which the last q_lens are this step's queries."""
     from pico_vllm_b200 import ops
     g = gen(20 + seed)
@@ -132,8 +132,11 @@ def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, se
             q[t_last, :hd] = (qv / qv.norm() * 6).to(dtype)
     out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
     scratch = None
-    if splits > 1:
-        scratch = torch.empty(ops.attention_scratch_floats(T, nh, hd, splits), dtype=torch.float32, device=DEV)
+    if splits > 1 or pair:
+        # pair (a number of keys): room for two partial results per (token, head), with which the tcgen05 prompt
+        # kernel lets two blocks share a query tile that sees at least that many keys
+        scratch = torch.full((ops.attention_scratch_floats(T, nh, hd, max(splits, 2)),), float("nan"), dtype=torch.float32,
+                             device=DEV)
     scale = 1.0 / math.sqrt(hd)
     if mma:
         cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
@@ -158,7 +161,8 @@ def _attention_case(dtype, nh, nkv, hd, ps, window, seg_lens, q_lens, splits, se
             assert maps[2] is not None and maps[3] is not None
         ops.paged_attention_mma(q.to(DEV), kd, vd, out, tok_seg.to(DEV), pos.to(DEV), table.to(DEV),
                                 cu.to(DEV), pf.to(DEV), len(pf), max([n for n in q_lens if n > 1], default=0),
-                                dec.to(DEV), len(dec), nh, nkv, hd, ps, window, scale, splits, scratch, *maps)
+                                dec.to(DEV), len(dec), nh, nkv, hd, ps, window, scale, splits, scratch, *maps,
+                                **({"pair_min_keys": pair} if pair else {}))
         if tma:
             torch.cuda.synchronize()
             assert ops.tma_status() == 0
@@ -247,28 +251,46 @@ def test_tma_attention_mixed_segments(nh, nkv, hd, ps, window):
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(6, 2, 64, 16), (12, 2, 128, 16), (7, 1, 128, 8), (16, 1, 64, 32), (4, 4, 128, 64),
                                           (28, 4, 128, 16), (3, 3, 64, 8)])
 @pytest.mark.parametrize("window", [None, 24, 200])
-def test_tcgen05_attention_mixed_segments(nh, nkv, hd, ps, window):
+@pytest.mark.parametrize("pair", [0, 128, 512])
+def test_tcgen05_attention_mixed_segments(nh, nkv, hd, ps, window, pair):
     got, want = _attention_case(torch.bfloat16, nh, nkv, hd, ps, window, seg_lens=[300, 133, 9, 1, 70, 2, 64, 190, 1000],
-                                q_lens=[257, 1, 2, 1, 33, 2, 1, 64, 700], splits=1, mma=True, tma=True, poison=True, tc=True)
+                                q_lens=[257, 1, 2, 1, 33, 2, 1, 64, 700], splits=1, mma=True, tma=True, poison=True, tc=True,
+                                pair=pair)
     assert torch.isfinite(got).all()
     assert torch.allclose(got, want, **MMA_TOL)
 
 
 @pytest.mark.parametrize("window", [None, 5000])
-def test_long_contexts_beyond_the_block_table_cache(window):
+@pytest.mark.parametrize("pair", [0, 4096])
+def test_long_contexts_beyond_the_block_table_cache(window, pair):
     """Contexts whose block tables are longer than what a block keeps in shared memory (256 entries in
     the decode kernel, 1024 in the prompt kernel): the entries beyond come straight from global memory."""
     got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[9100, 6000, 2100], q_lens=[300, 1, 1], splits=1,
-                                seed=7, spike=True, mma=True, tma=True, poison=True, tc=True)
+                                seed=7, spike=True, mma=True, tma=True, poison=True, tc=True, pair=pair)
     assert torch.isfinite(got).all()
     assert torch.allclose(got, want, **MMA_TOL)
 
 
 @pytest.mark.parametrize("window,q_lens", [(None, [200, 150]), (64, [200, 150]), (None, [2, 300]), (100, [517, 64])])
-def test_tcgen05_prefill_far_key_and_window_edge(window, q_lens):
+@pytest.mark.parametrize("pair", [0, 128])
+def test_tcgen05_prefill_far_key_and_window_edge(window, q_lens, pair):
     got, want = _attention_case(torch.bfloat16, 4, 2, 64, 8, window, seg_lens=[517, 300], q_lens=q_lens, splits=1,
-                                seed=5, spike=True, mma=True, tma=True, poison=True, tc=True)
+                                seed=5, spike=True, mma=True, tma=True, poison=True, tc=True, pair=pair)
     assert torch.allclose(got, want, **MMA_TOL)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(12, 2, 128, 16), (6, 3, 64, 32)])
+@pytest.mark.parametrize("window,seg_lens,q_lens", [(None, [2048], [2048]), (None, [6000, 700], [512, 700]),
+                                                    (1500, [3000], [1024]), (None, [513, 511, 2000], [513, 2, 1100])])
+def test_tcgen05_prefill_query_tiles_shared_by_two_blocks(nh, nkv, hd, ps, window, seg_lens, q_lens):
+    """Query tiles that see 512 keys or more are computed by two blocks, half of the keys each, and the block that
+    finishes last adds the two partial results: prompts around that size, portions late in a long context, a
+    window, several requests; twice, since the pairs' counters have to be zero again after a launch."""
+    for seed in (3, 4):
+        got, want = _attention_case(torch.bfloat16, nh, nkv, hd, ps, window, seg_lens=seg_lens, q_lens=q_lens, splits=1,
+                                    seed=seed, spike=True, mma=True, tma=True, poison=True, tc=True, pair=512)
+        assert torch.isfinite(got).all()
+        assert torch.allclose(got, want, **MMA_TOL)
 
 
 @pytest.mark.parametrize("window,splits", [(None, 1), (None, 8), (64, 1), (64, 4)])
