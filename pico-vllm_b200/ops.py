@@ -533,6 +533,10 @@ def skinny_qkv_rope_store(x: torch.Tensor, qkv_weight: torch.Tensor, bias: Optio
 
 # ------------------------------------------------------------------------------------------
 # Products for many tokens on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+# Measured for gate_up + SwiGLU at 17920 x 1536: the library product followed by the SwiGLU kernel takes 13.8 us at
+# 64 tokens, 15.0 at 128, 17.1 at 200, 18.6 at 256; the pair kernel 17.1 us anywhere up to 256 tokens; the one-SM
+# kernel 22.5 us from 128 to 255.  So the model's feed-forward takes the tcgen05 path from TC_PAIR_MIN_TOKENS = 200
+# tokens on, with the pair kernel; TC_MIN_TOKENS is what the kernels themselves take.
 TC_MIN_TOKENS = 128
 
 
@@ -550,7 +554,7 @@ def tc_status() -> int:
     return out.value | out2.value
 
 
-TC_PAIR_MIN_TOKENS = 256      # from here on two SMs share a tile (tcgen05.mma.cta_group::2)
+TC_PAIR_MIN_TOKENS = 200      # from here on two SMs share a tile (tcgen05.mma.cta_group::2), and the tcgen05 path pays
 
 
 def _tc_gemm(x, weight, out, residual, M, N, K, epi, pair, what):

@@ -43,8 +43,9 @@ class GatedMLP(Part):
             a = ops.skinny_gate_up_swiglu(residual, self.gate_up_weight, norm.weight, norm.eps)
         elif ops.skinny_takes(h, self.gate_up_weight) and self.inner % 8 == 0:
             a = ops.skinny_gate_up_swiglu(h, self.gate_up_weight)      # product and activation in one kernel
-        elif ops.tc_takes(h, self.gate_up_weight) and self.inner % 8 == 0:
-            # many tokens: tcgen05 product with the activation in its epilogue (the [T, 2I] buffer never exists)
+        elif h.shape[0] >= ops.TC_PAIR_MIN_TOKENS and ops.tc_takes(h, self.gate_up_weight) and self.inner % 8 == 0:
+            # many tokens: tcgen05 product with the activation in its epilogue (the [T, 2I] buffer never exists);
+            # below that the library product and the activation kernel are faster (measured, see ops)
             a = ops.tc_gate_up_swiglu(h, self.gate_up_weight)
         else:
             gu = ops.linear(h, self.gate_up_weight)

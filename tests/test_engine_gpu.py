@@ -74,7 +74,7 @@ def test_long_decoding(dtype, name):
 @pytest.mark.parametrize("name", ["a", "b", "d", "e"])
 def test_long_prompts_in_one_step(dtype, name):
     """Prompts of several hundred tokens, whole and as two requests in one step: in bfloat16 these
-    sizes go through the tcgen05 kernels (products from 128 tokens on, pairs of SMs from 256 on,
+    sizes go through the tcgen05 kernels (gate_up products on pairs of SMs from 200 tokens on,
     attention tiles of 128 rows with several key tiles)."""
     cfg = helpers.tiny_config(name)
     reqs = {"x": helpers.random_ids(700, cfg.vocab_size, 31), "y": helpers.random_ids(300, cfg.vocab_size, 32)}
