@@ -80,13 +80,17 @@ template <int NTHREADS> __device__ __forceinline__ void consumer_sync() {
     asm volatile("bar.sync 1, %0;\n" ::"n"(NTHREADS) : "memory");
 }
 
-// A tile is [64 cache positions][HD] bfloat16, rows of HD*2 bytes, made of 128-byte segments that
-// TMA stores in its 128-byte swizzle: the 16-byte piece c of segment number s (counted from the
-// tile's 1024-byte aligned start) sits at piece position c ^ (s & 7).
+// A tile is 64 cache positions = 64 / page_size pages, and a page arrives as one TMA box
+// [HD / 64 blocks of 64 dims][page_size positions][128 bytes] in the 128-byte swizzle: inside a block the
+// 16-byte piece c of position r sits at piece c ^ (r & 7) (a block starts on a multiple of 1024 bytes, since
+// page_size >= 8).  Consecutive positions are consecutive 128-byte rows, so the eight rows an ldmatrix reads
+// fall into eight different bank groups (with rows of HD * 2 bytes, position after position, they fell into four:
+// half of the shared-memory wavefronts of the kernel were bank conflicts).
 template <int HD>
-__device__ __forceinline__ uint32_t swz_addr(uint32_t tile, int key, int dim) {
-    const int seg = key * (HD / 64) + (dim >> 6), chunk = (dim & 63) >> 3;
-    return tile + seg * 128 + ((chunk ^ (seg & 7)) << 4);
+__device__ __forceinline__ uint32_t tile_off(int key, int dim, int page_size) {
+    const int pg = key / page_size, r = key - pg * page_size;
+    const int chunk = (dim & 63) >> 3;
+    return (uint32_t)(pg * page_size * HD * 2 + (dim >> 6) * page_size * 128 + r * 128 + ((chunk ^ (r & 7)) << 4));
 }
 
 // 4 consumer warps (multiply) + 1 producer warp (one lane issues the TMA copies).  full[s]: the
@@ -186,7 +190,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
                 const int e = it * ppt + pg;
                 const int page = e < TMA_TABLE_CACHE ? tbl_s[e] : table[n0 / page_size + pg];
                 const int row = (page * nkv + kh) * page_size;
-                tma_load_3d(kt + (lane & 1) * TILE_BYTES + pg * page_size * HD * 2, (lane & 1) ? &v_map : &k_map, 0, 0, row,
+                tma_load_3d(kt + (lane & 1) * TILE_BYTES + pg * page_size * HD * 2, (lane & 1) ? &v_map : &k_map, 0, row, 0,
                             full + s);
             }
         }
@@ -231,6 +235,14 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
         for (int k0 = 0; k0 < HD; k0 += 16) ldmatrix_x2(qf[nt][k0 / 16], smem_u32(q_s + (nt * 8 + b_row) * QLD + k0 + b_col));
 
+    // where this lane's rows of a tile sit does not change from tile to tile
+    const int kw = wq * 16;                                      // this warp's 16 positions of the tile
+    uint32_t k_off[HD / 16], v_off[HD / 16];
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) {
+        k_off[i] = tile_off<HD>(kw + a_row, i * 16 + a_col, page_size);
+        v_off[i] = tile_off<HD>(kw + v_row, i * 16 + v_col, page_size);
+    }
     for (int it = grp; it < ntiles; it += NG) {
         const int s = it % TMA_STAGES;
         const int n0 = (t_begin + it) * MMA_BN;
@@ -241,7 +253,6 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
         if (*abort_s) break;
         const uint32_t kt = smem_u32(tiles + (size_t)s * 2 * TILE_BYTES);
         const uint32_t vt = kt + TILE_BYTES;
-        const int kw = wq * 16;                                  // this warp's 16 positions of the tile
         const int w0 = n0 + kw;
         if (w0 < hi && w0 + 16 > lo) {
             // q.k: four independent accumulators per head tile (a tensor-core instruction waits more
@@ -254,7 +265,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
             for (int k0 = 0; k0 < HD; k0 += 16) {
                 uint32_t a[4];
-                ldmatrix_x4(a, swz_addr<HD>(kt, kw + a_row, k0 + a_col));
+                ldmatrix_x4(a, kt + k_off[k0 / 16]);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) mma_bf16(sc[nt][(k0 / 16) & 3], a, qf[nt][k0 / 16][0], qf[nt][k0 / 16][1]);
             }
@@ -301,7 +312,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
 #pragma unroll
             for (int d0 = 0; d0 < HD; d0 += 16) {
                 uint32_t a[4];
-                ldmatrix_x4_trans(a, swz_addr<HD>(vt, kw + v_row, d0 + v_col));
+                ldmatrix_x4_trans(a, vt + v_off[d0 / 16]);
                 if (warp_edge) {
                     // register j of lane L holds dims d0 + L/4 (+ 8 for odd j) of cache positions
                     // w0 + (j / 2) * 8 + (L % 4) * 2 + {0, 1} (low and high half): clear by position
@@ -439,7 +450,8 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // Fills `map_out` (128 bytes, 64-byte aligned host memory) with a tensor map over the cache pages of
 // one layer: a [rows, hd] bfloat16 matrix (rows = pages * kv_heads * page_size) read in boxes of
-// [page_size rows, hd elements] (one page of one head) with the 128-byte swizzle.  Returns 0, or PICO_ERR_SIZE for sizes
+// [page_size rows, hd elements] (one page of one head) with the 128-byte swizzle, the 64-element blocks of the
+// rows one after the other in shared memory.  Returns 0, or PICO_ERR_SIZE for sizes
 // the TMA kernels do not take, or -7 when the driver refuses.
 PICO_API int pico_make_kv_tensor_map(void* map_out, const void* base, long long rows, int hd, int page_size) {
     if (hd % 64 != 0 || hd < 64 || hd > 256 || page_size < 8 || page_size > MMA_BN || MMA_BN % page_size != 0 ||
@@ -447,11 +459,11 @@ PICO_API int pico_make_kv_tensor_map(void* map_out, const void* base, long long 
         return PICO_ERR_SIZE;
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return -7;
-    // dimensions: 64 elements of a 128-byte segment, the hd/64 segments of a row, the rows; one box is a
-    // whole page of one key/value head
-    const cuuint64_t dims[3] = {64, (cuuint64_t)(hd / 64), (cuuint64_t)rows};
-    const cuuint64_t strides[2] = {128, (cuuint64_t)hd * 2};
-    const cuuint32_t box[3] = {64, (cuuint32_t)(hd / 64), (cuuint32_t)page_size};
+    // dimensions: 64 elements of a 128-byte segment, the rows, the hd/64 segments of a row; one box is a
+    // whole page of one key/value head and arrives as [segment][row][128 bytes]
+    const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(hd / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)hd * 2, 128};
+    const cuuint32_t box[3] = {64, (cuuint32_t)page_size, (cuuint32_t)(hd / 64)};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
