@@ -1,11 +1,13 @@
 """The cache manager: keys and values in pages with a block table per request, groups of
 layers with pages of their own, and slots for per-request state of fixed size.
 
-Cache entries (one per layer call that keeps a cache) with the same needs (key/value heads,
-head size, window) form a *group*.  A group has its own page pool, its own block tables and one
-pair of device tensors [entries, num_pages, kv_heads, page_size, head_dim]; a page number means
+Cache entries (one per layer call that keeps a cache) with the same paged needs (for keys and
+values: heads, head size, window) form a *group*.  A group has its own page pool, its own block
+tables and, for every tensor its spec names, one device tensor [entries, num_pages, *page shape]
+(keys and values: [entries, num_pages, kv_heads, page_size, head_dim] each); a page number means
 the same page in every entry of the group, as one block id spans all layers in the reference
-(pico_vllm/blockmanager.py:39-42).  A request holds a *slot* (0..max_num_seqs-1) from admission
+(pico_vllm/blockmanager.py:39-42).  Which spec classes are paged and which are fixed-size state is
+looked up in ``cache/kinds.py``.  A request holds a *slot* (0..max_num_seqs-1) from admission
 to its end; the slot indexes the block tables and the fixed-size state tensors.
 
 Pages are taken when tokens are appended (``append``), given back when the request ends
@@ -24,19 +26,27 @@ import numpy as np
 import torch
 
 from ..errors import OutOfPages, PicoError, ScheduleError
-from ..parts.base import CacheView, FixedState, PagedKV
+from ..parts.base import CacheView
+from .kinds import kind_of
 from .pages import PagePool
 
 
 @dataclass
 class KVGroup:
-    spec: PagedKV
+    spec: object                       # a paged spec: page_tensors(page_size), window
     entries: List[int]                 # cache entry ids served by this group, in order
     pool: PagePool
     tables: np.ndarray                 # int32 [max_num_seqs, max_blocks]; -1 = no page
     first_block: np.ndarray            # int32 [max_num_seqs]; blocks below were given back
-    k: Optional[torch.Tensor] = None   # [len(entries), num_pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    tensors: Dict[str, torch.Tensor] = field(default_factory=dict)   # name -> [len(entries), num_pages, *page shape]
+
+    @property
+    def k(self) -> Optional[torch.Tensor]:
+        return self.tensors.get("k")
+
+    @property
+    def v(self) -> Optional[torch.Tensor]:
+        return self.tensors.get("v")
 
 
 class CacheManager:
@@ -51,9 +61,10 @@ class CacheManager:
         self.groups: List[KVGroup] = []
         self.entry_group: Dict[int, tuple] = {}     # entry id -> (group index, index inside the group)
         self.states: Dict[int, torch.Tensor] = {}   # entry id -> [max_num_seqs, *shape]
-        self.state_specs: Dict[int, FixedState] = {}
+        self.state_specs: Dict[int, object] = {}
         for eid, spec in enumerate(cache_entries):
-            if isinstance(spec, PagedKV):
+            kind = kind_of(spec)
+            if kind == "paged":
                 for gi, g in enumerate(self.groups):
                     if g.spec == spec:
                         self.entry_group[eid] = (gi, len(g.entries))
@@ -64,15 +75,13 @@ class CacheManager:
                     self.groups.append(KVGroup(spec, [eid], PagePool(num_pages),
                                                np.full((max_num_seqs, self.max_blocks), -1, np.int32),
                                                np.zeros(max_num_seqs, np.int32)))
-            elif isinstance(spec, FixedState):
-                self.state_specs[eid] = spec
             else:
-                raise PicoError(f"cache entry {eid}: unknown kind of cache need {spec!r}")
+                self.state_specs[eid] = spec
         if allocate:
             for g in self.groups:
-                shape = (len(g.entries), num_pages, g.spec.n_kv_heads, page_size, g.spec.head_dim)
-                g.k = torch.zeros(shape, dtype=dtype, device=self.device)
-                g.v = torch.zeros(shape, dtype=dtype, device=self.device)
+                for name, page_shape in g.spec.page_tensors(page_size).items():
+                    g.tensors[name] = torch.zeros((len(g.entries), num_pages) + tuple(page_shape), dtype=dtype,
+                                                  device=self.device)
             for eid, spec in self.state_specs.items():
                 self.states[eid] = torch.zeros((max_num_seqs,) + tuple(spec.shape),
                                                dtype=getattr(torch, spec.dtype), device=self.device)
@@ -84,8 +93,8 @@ class CacheManager:
     # ------------------------------------------------------------------ sizes
     def bytes_per_page(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.spec.n_kv_heads * self.page_size * g.spec.head_dim * item
-                   for g in self.groups)
+        return sum(len(g.entries) * int(np.prod(shape)) * item
+                   for g in self.groups for shape in g.spec.page_tensors(self.page_size).values())
 
     @property
     def free_slots(self) -> int:
@@ -122,10 +131,10 @@ class CacheManager:
 
     def _give_back(self, g: KVGroup, pages: List[int]) -> None:
         freed = g.pool.release(pages)
-        if self.poison_freed and freed and g.k is not None:
+        if self.poison_freed and freed and g.tensors:
             idx = torch.tensor(freed, dtype=torch.long, device=self.device)
-            g.k[:, idx] = float("nan")
-            g.v[:, idx] = float("nan")
+            for t in g.tensors.values():
+                t[:, idx] = float("nan")
 
     # ------------------------------------------------------------------ pages for new tokens
     def _blocks_missing(self, g: KVGroup, slot: int, new_len: int) -> int:
@@ -216,9 +225,10 @@ class CacheManager:
             if eid in self.entry_group:
                 gi, idx = self.entry_group[eid]
                 g = self.groups[gi]
-                view = CacheView(group=gi, k=None if g.k is None else g.k[idx],
-                                 v=None if g.v is None else g.v[idx], page_size=self.page_size)
-                if g.k is not None and g.k.is_cuda and g.k.dtype == torch.bfloat16:
+                mine = {name: t[idx] for name, t in g.tensors.items()}
+                view = CacheView(group=gi, k=mine.get("k"), v=mine.get("v"), page_size=self.page_size, tensors=mine)
+                if view.k is not None and view.v is not None and view.k.is_cuda and view.k.dtype == torch.bfloat16 \
+                        and view.k.dim() == 4 and view.k.shape == view.v.shape:
                     from .. import ops
                     view.k_map, view.v_map = ops.make_kv_tensor_map(view.k), ops.make_kv_tensor_map(view.v)
                     view.k_map2d, view.v_map2d = ops.make_kv_tensor_map_2d(view.k), ops.make_kv_tensor_map_2d(view.v, values=True)

@@ -230,9 +230,12 @@ PICO_API int pico_paged_attention_noalloc(const void* q, int q_row_stride, const
                                           int err_len) {
     if (err && err_len > 0) err[0] = 0;
     if (T <= 0) return 0;
-    if (nh <= 0 || hd <= 0 || n_splits < 1)
-        return noalloc_fail(PICO_ERR_SIZE, err, err_len, "nh, hd and n_splits must be positive");
-    const long long need = (long long)T * nh * n_splits * (hd + 2);
+    // the same limits as pico_paged_attention_generic, checked first so that the product below cannot wrap
+    if (nh <= 0 || nkv <= 0 || nkv > 65535 || nh % nkv != 0 || hd % 16 != 0 || hd < 16 || hd > 32 * ATT_MAX_DPL ||
+        n_splits < 1 || n_splits > 65535)
+        return noalloc_fail(PICO_ERR_SIZE, err, err_len, "a size the attention kernels do not take");
+    // one part per token needs no scratch at all: the kernel writes its result straight to out
+    const long long need = n_splits == 1 ? 0 : (long long)T * nh * n_splits * (hd + 2);
     if (need > (long long)PICO_NOALLOC_SCRATCH_FLOATS) {
         char msg[200];
         snprintf(msg, sizeof msg,

@@ -87,7 +87,7 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
             except (OSError, ValueError):
                 pass
     if not build_if_needed:
-        raise KernelError("the CUDA kernels are not built (run __graft_entry__.build())")
+        raise KernelError("the CUDA kernels are not built (call pico_vllm_b200.csrc.build())")
     return build(verbose=verbose)
 
 

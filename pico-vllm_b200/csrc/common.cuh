@@ -67,6 +67,19 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 static inline int pico_launch_status() { return (int)cudaGetLastError(); }
 
+// Multiprocessors of the current device (asked once per device; grids are sized from it).
+static inline int pico_num_sms() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] <= 0) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 1;
+        cached[dev] = sms;
+    }
+    return cached[dev];
+}
+
 // Programmatic dependent launch: every kernel of this library is launched with the attribute that
 // lets it start while the kernel before it in the stream is still draining, and therefore begins
 // with pdl_launch_dependents() (the next kernel may be scheduled) and calls pdl_wait() before it

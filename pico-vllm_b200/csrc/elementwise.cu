@@ -185,14 +185,16 @@ PICO_API int pico_swiglu(const void* gate_up, void* out, int T, int I, int act_d
     if (act_dtype == PICO_BF16 && I % 8 == 0) {
         const size_t total8 = (size_t)T * (I / 8);
         size_t want8 = (total8 + 255) / 256;
-        const int blocks8 = (int)(want8 > 148 * 16 ? 148 * 16 : want8);
+        const long long cap = 16LL * pico_num_sms();
+        const int blocks8 = (int)((long long)want8 > cap ? cap : (long long)want8);
         pico_launch(swiglu_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, I, total8);
         return pico_launch_status();
     }
     const size_t total = (size_t)T * I;
     const int threads = 256;
     size_t want = (total + threads - 1) / threads;
-    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    const long long cap1 = 16LL * pico_num_sms();
+    const int blocks = (int)((long long)want > cap1 ? cap1 : (long long)want);
     if (act_dtype == PICO_F32)
         pico_launch((swiglu_kernel<float>), dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total);
     else if (act_dtype == PICO_BF16)

@@ -389,15 +389,7 @@ static int tp_make_map(CUtensorMap* map, const void* base, long long rows, int K
     return r == CUDA_SUCCESS ? 0 : -7;
 }
 
-static int tp_num_sms() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
+static int tp_num_sms() { return pico_num_sms(); }
 
 template <int BN, int EPI, int MB>
 static int tp_launch(const void* x, int ldx, const void* w, const TpArgs& a, cudaStream_t stream) {

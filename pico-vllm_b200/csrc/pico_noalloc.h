@@ -31,7 +31,8 @@ extern "C" {
 //
 // Returns 0 when the kernels were launched.  Returns a negative code and writes a message into
 // err (if err != NULL and err_len > 0) when the call is refused: -3 for a size the kernels do
-// not take, -5 when T * nh * n_splits * (hd + 2) exceeds PICO_NOALLOC_SCRATCH_FLOATS, -6 when
+// not take, -5 when n_splits > 1 and T * nh * n_splits * (hd + 2) exceeds
+// PICO_NOALLOC_SCRATCH_FLOATS (with n_splits == 1 no scratch is used and any T is taken), -6 when
 // the address of the scratch array could not be obtained.  A positive value is the cudaError_t
 // of a failed launch.
 //

@@ -324,11 +324,12 @@ PICO_API int pico_sample(const float* logits, int row_stride, int R, int V, cons
     if (R <= 0) return 0;
     if (V <= 0) return PICO_ERR_SIZE;
     if (temperature && !uniform) return PICO_ERR_SIZE;
+    const int wave = 2 * pico_num_sms();
     for (int r0 = 0; r0 < R; r0 += SAMPLE_ROWS) {
         const int rows = R - r0 < SAMPLE_ROWS ? R - r0 : SAMPLE_ROWS;
         // parts of at least 2048 entries, as many as give every SM a block or two
         int parts = 1;
-        while (parts < SAMPLE_MAX_PARTS && parts * 2 * 2048 <= V && parts * rows < 296) parts *= 2;
+        while (parts < SAMPLE_MAX_PARTS && parts * 2 * 2048 <= V && parts * rows < wave) parts *= 2;
         const int per = (V + parts - 1) / parts;
         const float* lg = logits + (size_t)r0 * row_stride;
         const dim3 grid(parts, rows), block(SAMPLE_THREADS);
@@ -344,20 +345,5 @@ PICO_API int pico_sample(const float* logits, int row_stride, int R, int V, cons
             pico_launch(sample_pick_kernel, grid, block, 0, stream, lg, row_stride, V, uniform + r0, out + r0, per);
         }
     }
-    return pico_launch_status();
-}
-
-// float32 copy of bfloat16 rows (logits of the bfloat16 path are handed out as float32)
-__global__ void bf16_to_f32_kernel(const bf16* __restrict__ in, float* __restrict__ out, size_t n) {
-    pdl_launch_dependents();
-    pdl_wait();
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-        out[i] = __bfloat162float(in[i]);
-}
-PICO_API int pico_bf16_to_f32(const void* in, float* out, long long n, cudaStream_t stream) {
-    if (n <= 0) return 0;
-    long long want = (n + 255) / 256;
-    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
-    pico_launch(bf16_to_f32_kernel, dim3(blocks), dim3(256), 0, stream, (const bf16*)in, out, (size_t)n);
     return pico_launch_status();
 }

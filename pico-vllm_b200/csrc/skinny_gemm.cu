@@ -407,15 +407,7 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
 // Do the activations of all of K fit in shared memory beside the weight rings (two blocks per SM)?
 static bool sg_xpre(int mt, int K) { return (size_t)mt * 8 * (K + 72) * sizeof(bf16) <= (mt == 1 ? 34 : 52) * 1024; }
 
-static int sg_num_sms() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
+static int sg_num_sms() { return pico_num_sms(); }
 
 template <int MT, int EPI, int STAGES, bool XPRE>
 static void sg_launch_one(const SkinnyArgs& a, int tiles, int grid, cudaStream_t stream) {

@@ -34,10 +34,10 @@ class Batch:
     groups: Dict[int, GroupBatch]
     q_lens: List[int]            # host copy: tokens of each segment
     kv_lens: List[int]           # host copy: length of each segment's request after this step
-    attn_splits: int = 1         # parts each token's key range is cut into
-    scratch: Optional[torch.Tensor] = None   # float32 scratch for split attention
-    pair_min_keys: int = 0       # > 0: prompt attention gives every query tile two blocks, which share a tile that sees
-                                 # at least this many keys (the scratch then holds two partial results per token and head)
+    # what each mixer planned for this step (Part.plan), by the mixer's plan_key(), and the float32 scratch
+    # that the step function provides for all of them (the largest any plan asked for; None if none did)
+    plans: Dict[object, object] = field(default_factory=dict)
+    scratch: Optional[torch.Tensor] = None
     decode_only: bool = False
     # the batch split for kernels that treat portions and single tokens differently
     prefill_segs: Optional[torch.Tensor] = None   # int32: segments with two or more tokens (None: all)
@@ -47,3 +47,7 @@ class Batch:
     num_decode_tokens: int = 0
     # tokens chosen by the sampling kernel in the step before; a token id -(j+1) in token_ids means feedback[j]
     feedback: Optional[torch.Tensor] = None
+
+    def plan(self, mixer):
+        """The plan ``mixer.plan(shape)`` returned for this step, or None."""
+        return self.plans.get(mixer.plan_key())

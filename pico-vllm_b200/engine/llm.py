@@ -18,6 +18,7 @@ from typing import Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
+from .. import ops
 from ..config.engine import EngineConfig
 from ..errors import ConfigError, ScheduleError
 from ..sampling import Sampler, SamplingParams, uniform_for
@@ -126,8 +127,14 @@ class LLM:
 
     # ------------------------------------------------------------------ inside
     def _step(self) -> List[Request]:
-        if self.cfg.async_scheduling:
-            return self._step_ahead()
+        done = self._step_ahead() if self.cfg.async_scheduling else self._step_in_turn()
+        if done:
+            # tokens leave the engine when a request completes: before that, make sure that no kernel gave up
+            # a bounded wait on the way (it would have left part of a result unwritten)
+            ops.check_kernel_status()
+        return done
+
+    def _step_in_turn(self) -> List[Request]:
         plan = self.scheduler.schedule()
         if not plan:
             return []

@@ -26,6 +26,7 @@ from .. import ops
 from ..cache.manager import CacheManager
 from ..config.engine import EngineConfig
 from ..errors import PicoError, ScheduleError
+from ..parts.base import StepShape
 from .batch import Batch, GroupBatch
 
 
@@ -85,7 +86,8 @@ class ModelRunner:
         self.device = cache.device
         self.on_gpu = self.device.type == "cuda"
         self.views = cache.views()
-        self._graphs: dict = {}          # decode bucket, or ("prefill", tokens, wanted rows) -> recorded step
+        # ("decode", bucket, plans' key) or ("prefill", tokens, wanted rows, plans' key) -> recorded step
+        self._graphs: dict = {}
         g = cfg.graph_prefill_tokens
         if g is None:
             g = min(cfg.prefill_chunk or cfg.max_num_batched_tokens, cfg.max_num_batched_tokens)
@@ -97,16 +99,13 @@ class ModelRunner:
         # where the sampling kernel leaves the tokens of a step for the next step's embedding
         self.feedback = torch.zeros(max(64, cache.max_num_seqs, max(cfg.graph_batch_sizes)), dtype=torch.int32,
                                     device=self.device)
-        kv = [g.spec for g in cache.groups]
-        self._max_heads = 0
-        for blk in model.blocks:
-            m = blk.mixer
-            if hasattr(m, "n_heads"):
-                self._max_heads = max(self._max_heads, m.n_heads * (m.head_dim + 2))
-        self._min_kv_heads = min((s.n_kv_heads for s in kv), default=1)
-        # query heads of a layer: what one token adds to the 128-row query tiles of prompt attention
-        self._tile_load = max((blk.mixer.n_heads for blk in model.blocks if hasattr(blk.mixer, "n_heads")), default=1)
         self._num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.on_gpu else 1
+        # one planner per distinct plan_key() among the mixers (layers of equal sizes share a plan)
+        self._planners: Dict[object, object] = {}
+        for blk in model.blocks:
+            mixer = getattr(blk, "mixer", None)
+            if mixer is not None and hasattr(mixer, "plan") and hasattr(mixer, "plan_key"):
+                self._planners.setdefault(mixer.plan_key(), mixer)
 
     # ------------------------------------------------------------------ buffers
     def _staging(self, n: int) -> _Staging:
@@ -116,37 +115,24 @@ class ModelRunner:
             self._stage = _Staging(max(n, 4096), self.device)
         return self._stage
 
-    def _splits(self, T: int, max_kv: int) -> int:
-        """How many parts to cut each token's key range into: a power of two (the parts of one token
-        and kv head run as one thread-block cluster): up to 16 when that still is at most one block
-        per SM, else up to 8 while the blocks make no more than one wave (two per SM on 148 SMs);
-        each part at least two tiles of 64 keys."""
-        groups = max(1, T * self._min_kv_heads)
-        want = 16 if groups * 16 <= 148 else min(296 // groups, 8)
-        want = min(want, max_kv // 128)
-        splits = 1
-        while splits * 2 <= want:
-            splits *= 2
-        return splits
+    def _plan(self, q_lens: List[int], starts: List[int], T: int, S: int):
+        """Asks every planner for its plan of this step.  Returns (plans by plan key, a hashable key of
+        all of them, float32 elements of scratch the largest of them needs)."""
+        shape = StepShape(num_tokens=T, num_segments=S, q_lens=q_lens, starts=starts,
+                          max_kv=max(st + n for st, n in zip(starts, q_lens)),
+                          decode_only=all(n == 1 for n in q_lens), num_sms=self._num_sms, engine=self.cfg)
+        plans, need = {}, 0
+        for key, mixer in self._planners.items():
+            plan = mixer.plan(shape)
+            if plan is not None:
+                plans[key] = plan
+                need = max(need, int(plan.scratch_floats))
+        return plans, tuple((repr(k), p.key) for k, p in plans.items()), need
 
-    def _pair_min_keys(self, q_lens: List[int], starts: List[int]) -> int:
-        """Whether prompt attention should give every query tile two blocks (the threshold in keys, or 0): only
-        when every portion of the step comes after a long context, where a tile takes long enough to pay for the
-        pair, and when the tiles are too few to keep the SMs busy by themselves (under two per SM)."""
-        m = self.cfg.pair_min_context
-        if not (m > 0 and q_lens and self.on_gpu and self.cfg.dtype == "bfloat16" and min(starts) >= m):
-            return 0
-        tiles = len(q_lens) * self._tile_load * -(-max(q_lens) // 128)
-        return m if tiles <= 2 * self._num_sms else 0
-
-    def _scratch_for(self, T: int, splits: int, pairs: bool = False) -> Optional[torch.Tensor]:
-        """Float32 scratch of the attention kernels: partial results of the parts of a single token's key
-        range, and two per (token, head) for query tiles of prompts that two blocks share."""
-        if pairs:
-            splits = max(splits, 2)
-        if splits <= 1:
+    def _scratch_for(self, need: int) -> Optional[torch.Tensor]:
+        """The step function's float32 scratch, grown when a plan asks for more."""
+        if need <= 0:
             return None
-        need = T * splits * self._max_heads
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
         return self._scratch
@@ -214,11 +200,11 @@ class ModelRunner:
         return logits
 
     def _build(self, items: Sequence[StepItem], starts: List[int], pad_to: Optional[int],
-               splits: Optional[int] = None, buffers=None, scratch=None, rows: Optional[int] = None,
-               pair: Optional[int] = None) -> Batch:
+               buffers=None, scratch=None, rows: Optional[int] = None, plans=None) -> Batch:
         """Index arrays of the step on the device.  ``pad_to``: number of one-token segments of
         a graph bucket (the batch is padded to it and the block tables keep their full width);
-        ``buffers``/``scratch``: the bucket's own staging and scratch tensors, which must not move."""
+        ``buffers``/``scratch``/``plans``: a recorded shape's own staging and scratch tensors, which must
+        not move, and the mixers' plans it was recorded with."""
         cache = self.cache
         S_real = len(items)
         q_lens = [len(it.tokens) for it in items]
@@ -291,16 +277,13 @@ class ModelRunner:
             return dev[off:off + n]
         groups = {gi: GroupBatch(d(lay.g_slots[gi], T), d(lay.g_tables[gi], S * W).view(S, W))
                   for gi in range(len(cache.groups))}
-        max_kv = max(kv_lens)
-        if splits is None:
-            splits = self._splits(T, max_kv)
-        pair_min = self._pair_min_keys([q_lens[i] for i in pf], [starts[i] for i in pf]) if pair is None else pair
+        if plans is None:
+            plans, _, need = self._plan(q_lens, starts, T, S)
+            scratch = self._scratch_for(need)
         return Batch(num_tokens=T, num_segments=S, token_ids=d(lay.token_ids, T), positions=d(lay.positions, T),
                      tok_seg=d(lay.tok_seg, T), seg_slots=d(lay.seg_slots, S), cu_q=d(lay.cu_q, S + 1),
                      logit_rows=d(lay.logit_rows, R), num_logit_rows=R, groups=groups, q_lens=q_lens,
-                     kv_lens=kv_lens, attn_splits=splits,
-                     scratch=scratch if scratch is not None else self._scratch_for(T, splits, pair_min > 0),
-                     pair_min_keys=pair_min,
+                     kv_lens=kv_lens, plans=plans, scratch=scratch,
                      decode_only=all(n == 1 for n in q_lens),
                      prefill_segs=d(lay.prefill_segs, len(pf)) if len(pf) < S else None, num_prefill_segs=len(pf),
                      max_prefill_q=max([q_lens[i] for i in pf], default=0),
@@ -315,16 +298,18 @@ class ModelRunner:
         B = self._bucket(len(items))
         # every segment has one token; logits are computed for every row of the bucket
         full = [StepItem(it.slot, it.tokens, (0,)) for it in items]
-        entry = self._graphs.get(B)
+        # a recorded step holds for one set of plans: as contexts grow a bucket may be recorded a few times
+        # (for attention: once per number of splits of the key range)
+        plans, plan_key, need = self._plan([1] * len(items), starts, B, B)
+        entry = self._graphs.get(("decode", B, plan_key))
         if entry is None:
-            entry = self._capture(B, full, starts)
+            logits = self._record(("decode", B, plan_key), full, starts, B, B, plans, need)
         else:
-            self._build(full, starts, pad_to=B, splits=entry["splits"], buffers=entry["buffers"],
-                        scratch=entry["scratch"])
+            self._build(full, starts, pad_to=B, buffers=entry["buffers"], scratch=entry["scratch"], plans=entry["plans"])
             entry["graph"].replay()
             ops._count(entry["launches"])
+            logits = entry["logits"]
         self.graph_replays += 1
-        logits = entry["logits"]
         rows = [i for i, it in enumerate(items) if len(it.want)]
         if len(rows) == len(items):
             return logits[:len(items)]
@@ -332,54 +317,44 @@ class ModelRunner:
 
     def _step_prefill_graph(self, items: Sequence[StepItem], starts: List[int]) -> torch.Tensor:
         """One full portion of one prompt: the same work every time but for the index arrays, so it is
-        recorded once (per number of wanted rows, 0 or 1) and replayed over its own staging buffers."""
+        recorded once (per number of wanted rows, 0 or 1, and per set of plans) and replayed over its own
+        staging buffers."""
         T, R = len(items[0].tokens), len(items[0].want)
-        pair = self._pair_min_keys([T], starts)
-        key = ("prefill", T, R, pair)
-        entry = self._graphs.get(key)
+        plans, plan_key, need = self._plan([T], starts, T, 1)
+        entry = self._graphs.get(("prefill", T, R, plan_key))
         if entry is None:
-            lay = _Layout(T, 1, R, len(self.cache.groups), self.cache.max_blocks)
-            buffers = _Staging(lay.total, self.device)
-            # a graph keeps the addresses it was recorded with: staging and attention scratch are its own
-            scratch = torch.empty(2 * T * self._max_heads, dtype=torch.float32, device=self.device) if pair else None
-            batch = self._build(items, starts, pad_to=1, splits=1, buffers=buffers, scratch=scratch, rows=R, pair=pair)
-            self.model.forward(batch, self.views)       # eager warm-up; writes the same cache rows
-            torch.cuda.synchronize(self.device)
-            graph = torch.cuda.CUDAGraph()
-            before = ops.launches
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(batch, self.views)
-            entry = {"graph": graph, "logits": logits, "launches": ops.launches - before, "batch": batch,
-                     "buffers": buffers, "scratch": scratch}
-            self._graphs[key] = entry
-            graph.replay()
+            logits = self._record(("prefill", T, R, plan_key), items, starts, 1, R, plans, need)
         else:
-            self._build(items, starts, pad_to=1, splits=1, buffers=entry["buffers"], scratch=entry["scratch"], rows=R,
-                        pair=pair)
+            self._build(items, starts, pad_to=1, buffers=entry["buffers"], scratch=entry["scratch"], rows=R,
+                        plans=entry["plans"])
             entry["graph"].replay()
             ops._count(entry["launches"])
+            logits = entry["logits"]
         self.graph_replays += 1
-        return entry["logits"]
+        return logits
 
-    def _capture(self, B: int, items: Sequence[StepItem], starts: List[int]) -> dict:
-        """First decode step at this bucket: run it once eagerly (this also warms up the
-        libraries), then record the same work into a graph over the same buffers."""
-        # a graph keeps the addresses it was recorded with: the bucket owns its staging and scratch
-        lay = _Layout(B, B, B, len(self.cache.groups), self.cache.max_blocks)
+    def _record(self, key, items: Sequence[StepItem], starts: List[int], S: int, R: int, plans, need: int) -> torch.Tensor:
+        """First step of a shape: a graph keeps the addresses it was recorded with, so the shape owns its
+        staging buffer and its scratch."""
+        T = sum(len(it.tokens) for it in items) + (S - len(items))
+        lay = _Layout(T, S, R, len(self.cache.groups), self.cache.max_blocks)
         buffers = _Staging(lay.total, self.device)
-        splits = self._splits(B, min(self.cache.max_seq_len, 4096))
-        scratch = (torch.empty(B * splits * self._max_heads, dtype=torch.float32, device=self.device)
-                   if splits > 1 else None)
-        batch = self._build(items, starts, pad_to=B, splits=splits, buffers=buffers, scratch=scratch)
-        self.model.forward(batch, self.views)           # eager warm-up; writes the same cache rows
+        scratch = torch.empty(need, dtype=torch.float32, device=self.device) if need > 0 else None
+        batch = self._build(items, starts, pad_to=S, buffers=buffers, scratch=scratch, rows=R, plans=plans)
+        return self._run_and_record(key, batch, {"buffers": buffers, "scratch": scratch, "plans": plans})
+
+    def _run_and_record(self, key, batch: Batch, entry: dict) -> torch.Tensor:
+        """The first step of a shape: runs it once, directly (this is the step itself, and it warms up the
+        libraries), then records the same work into a graph over the same buffers.  Recording executes
+        nothing and the recorded graph is not replayed here: the step's work happens exactly once, so a
+        mixer that advances per-request state of its own is stepped once, like the cache.  Returns
+        the direct run's logits."""
+        logits = self.model.forward(batch, self.views)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
         with torch.cuda.graph(graph):
-            logits = self.model.forward(batch, self.views)
-        launches = ops.launches - before
-        graph.replay()
-        entry = {"graph": graph, "logits": logits, "splits": splits, "launches": launches, "batch": batch,
-                 "buffers": buffers, "scratch": scratch}
-        self._graphs[B] = entry
-        return entry
+            recorded = self.model.forward(batch, self.views)
+        entry.update(graph=graph, logits=recorded, launches=ops.launches - before, batch=batch)
+        self._graphs[key] = entry
+        return logits

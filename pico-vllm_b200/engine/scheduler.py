@@ -50,6 +50,7 @@ class Request:
     num_computed: int = 0          # tokens of prompt + generated that are in the cache
     preemptions: int = 0
     finish_reason: Optional[str] = None
+    in_flight: int = 0             # launched steps of this request whose tokens the host has not read yet
 
     @property
     def all_ids(self) -> List[int]:
@@ -89,6 +90,7 @@ class Scheduler:
         self.running: List[Request] = []       # in order of admission: oldest first
         self.finished: List[Request] = []
         self.draining: List[Request] = []      # their last token is being computed; not scheduled again
+        self.lingering: List[Request] = []     # ended by their end token while a later step of theirs was in flight
         self.num_preemptions = 0
 
     # ------------------------------------------------------------------ requests in and out
@@ -106,6 +108,12 @@ class Scheduler:
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running or self.draining)
+
+    def _held_in_flight(self) -> bool:
+        """True while requests that will not be scheduled again still hold pages or a slot, because a
+        launched step of theirs has not been read yet (one step ahead of the device): what they hold
+        comes back at the next ``resolve``, so "the cache to itself" cannot be judged before that."""
+        return any(r.slot is not None for r in self.draining) or any(r.slot is not None for r in self.lingering)
 
     def _preempt(self, request: Request) -> None:
         self.cache.release(request.slot)
@@ -153,6 +161,8 @@ class Scheduler:
                             n -= 1
                         if fits(req, n):
                             break
+                        if self._held_in_flight():
+                            return plan         # empty: the caller reads the step in flight, then asks again
                         raise OutOfPages(f"request {req.request_id} cannot go on even with the cache to itself "
                                          f"({req.total_len} tokens; {self.cache.num_pages} pages of "
                                          f"{self.cache.page_size})")
@@ -190,7 +200,7 @@ class Scheduler:
                     # not enough pages now; wait for running requests to finish
                     self.cache.release(slot)
                     req.slot = None
-                    if not self.running and not plan:
+                    if not self.running and not plan and not self._held_in_flight():
                         raise OutOfPages(f"request {req.request_id} does not fit the cache even alone")
                     break
             self.waiting.popleft()
@@ -206,7 +216,9 @@ class Scheduler:
     # ``resolve`` puts the values in when they arrive and finishes requests.  A request that ends by
     # its token count is known at ``advance`` and is not scheduled again; one that ends by its end
     # token has by then been launched once more: that work is thrown away, and its pages and slot are
-    # given back only when ``resolve`` is called for that later step (``release_when_idle``).
+    # given back only when ``resolve`` is called for that later step (until then it is in ``lingering``).  While
+    # such a request, or one in ``draining``, still holds pages, ``schedule`` does not judge that a request "does
+    # not fit even alone": it returns what it has (maybe nothing) and the caller asks again after ``resolve``.
     def advance(self, plan: Sequence[Scheduled]) -> None:
         j = 0
         for s in plan:
@@ -216,7 +228,7 @@ class Scheduler:
                 continue
             req.generated_ids.append(-(j + 1))
             j += 1
-            req.in_flight = getattr(req, "in_flight", 0) + 1
+            req.in_flight += 1
             if len(req.generated_ids) >= req.max_new_tokens or req.total_len >= self.cache.max_seq_len:
                 # the last token is on its way: nothing more to compute for this request
                 req.finish_reason = "length" if len(req.generated_ids) >= req.max_new_tokens else "cache_length"
@@ -236,6 +248,7 @@ class Scheduler:
                 if req.in_flight == 0 and req.slot is not None:
                     self.cache.release(req.slot)
                     req.slot = None
+                    self.lingering.remove(req)
                 continue
             # the oldest placeholder of this request is this step's token
             at = next(i for i, t in enumerate(req.generated_ids) if t < 0)
@@ -245,10 +258,8 @@ class Scheduler:
             if hit_eos or (last and req in self.draining):
                 if hit_eos:
                     req.finish_reason = "eos"
-                    dropped = len(req.generated_ids) - at - 1        # tokens launched after the end token
-                    del req.generated_ids[at + 1:]
+                    del req.generated_ids[at + 1:]      # placeholders of steps launched after the end token
                     req.num_computed = min(req.num_computed, req.total_len)
-                    _ = dropped
                 req.status = RequestStatus.FINISHED
                 if req in self.running:
                     self.running.remove(req)
@@ -259,6 +270,8 @@ class Scheduler:
                 if req.in_flight == 0 and req.slot is not None:
                     self.cache.release(req.slot)
                     req.slot = None
+                elif req.slot is not None:
+                    self.lingering.append(req)
                 self.finished.append(req)
                 done.append(req)
         return done

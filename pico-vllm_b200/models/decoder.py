@@ -34,8 +34,13 @@ class Binding:
 
 class DecoderModel:
     def __init__(self, config, embed: Part, blocks: Sequence, order: Sequence[LayerCall], final_norm: Part,
-                 head: Part, bindings: List[Binding]):
+                 head: Part, bindings: List[Binding], embed_position: Optional[Part] = None):
+        """``embed_position``: a position encoding that acts on the residual stream right after the
+        embedding (absolute or learned positions): a part with ``add_to(x, positions) -> x`` for the
+        float32 stream x [T, width] and int32 positions [T] (-1: a padding row).  Rotary encodings are
+        not given here: they belong to the mixer that rotates with them."""
         self.config = config
+        self.embed_position = embed_position
         self.embed, self.blocks, self.order = embed, list(blocks), list(order)
         self.final_norm, self.head, self.bindings = final_norm, head, bindings
         self.vocab_size = head.vocab
@@ -70,7 +75,7 @@ class DecoderModel:
         return [entries[i] for i in range(len(entries))]
 
     def all_parts(self) -> List[Part]:
-        parts = [self.embed]
+        parts = [self.embed] + ([self.embed_position] if self.embed_position is not None else [])
         for b in self.blocks:
             parts.extend(b.parts().values())
         parts += [self.final_norm, self.head]
@@ -85,6 +90,8 @@ class DecoderModel:
         """Runs the batch's tokens through every call of the order; returns float32 logits
         [len(batch.logit_rows), vocab]."""
         x = self.embed.forward(batch.token_ids, batch.feedback)
+        if self.embed_position is not None:
+            x = self.embed_position.add_to(x, batch.positions)
         pending = None
         for call in self.order:
             view = None

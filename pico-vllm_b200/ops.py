@@ -69,12 +69,9 @@ def library():
         "pico_paged_prefill_tcgen05": [vp, vp, vp, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32,
                                        vp, i32, vp, i32, vp],
         "pico_tca_status": [vp],
-        "pico_gemm_tcgen05": [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp],
-        "pico_tc_status": [vp],
         "pico_gemm_tcgen05_pair": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp],
         "pico_tp_status": [vp],
         "pico_sample": [vp, i32, i32, i32, vp, vp, vp, vp, vp],
-        "pico_bf16_to_f32": [vp, vp, i64, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -176,8 +173,9 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 def rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
                inv_freq: torch.Tensor, slots: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
                v_pages: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, head_dim: int,
-               page_size: int) -> None:
+               page_size: int, pairing: str = "half") -> None:
     """Adds the bias, rotates q (in place) and k, and stores k and v into their cache pages.
+    ``pairing``: which dims rotate together; the kernels have "half" only (d with d + head_dim/2).
 
     qkv [T, (n_heads + 2 n_kv_heads) head_dim]; bias float32 or None; positions, slots int32 [T]
     (slot = page * page_size + offset, -1 = do not store); inv_freq float32 [rot_dim / 2];
@@ -185,6 +183,7 @@ def rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch
     is rotated.
     """
     _cuda(qkv, bias, positions, inv_freq, slots, k_pages, v_pages)
+    _check_pairing(pairing, "rope_store")
     T = qkv.shape[0]
     width = (n_heads + 2 * n_kv_heads) * head_dim
     if qkv.shape[1] != width or qkv.stride(1) != 1:
@@ -204,6 +203,11 @@ def rope_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch
                                      head_dim, 2 * inv_freq.shape[0], page_size, _dtype_code(qkv), _stream()),
            f"rope_store (head_dim {head_dim})")
     _count()
+
+
+def _check_pairing(pairing: str, what: str) -> None:
+    if pairing != "half":
+        raise KernelError(f"{what}: rotary pairing {pairing!r} is not built (the kernels pair dim d with d + head_dim/2)")
 
 
 def attention_scratch_floats(T: int, n_heads: int, head_dim: int, n_splits: int) -> int:
@@ -308,6 +312,20 @@ def tma_status() -> int:
     out = ctypes.c_int(0)
     library().pico_tma_status(ctypes.addressof(out))
     return out.value
+
+
+def check_kernel_status() -> None:
+    """Raises KernelError when a kernel gave up a bounded wait (on a TMA copy or a tensor-core barrier)
+    since the library was loaded: such a block leaves its part of the result unwritten, so the
+    tokens computed since are not to be trusted.  Reads three status words from the device (a few
+    synchronous 4-byte copies); does nothing before the library was first used."""
+    if _lib is None:
+        return
+    bad = [name for name, word in (("paged_decode_tma (decode attention)", tma_status()),
+                                   ("paged_prefill_tcgen05 (prompt attention)", tca_status()),
+                                   ("gemm_tcgen05_pair (feed-forward product)", tc_status())) if word]
+    if bad:
+        raise KernelError("a bounded wait ran out in: " + ", ".join(bad) + "; results since then are invalid")
 
 
 _PAIR_COUNTERS = {}
@@ -500,11 +518,13 @@ def skinny_qkv_rope_store(x: torch.Tensor, qkv_weight: torch.Tensor, bias: Optio
                           positions: torch.Tensor, inv_freq: torch.Tensor, slots: Optional[torch.Tensor],
                           k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], n_heads: int,
                           n_kv_heads: int, head_dim: int, page_size: int,
-                          norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
+                          norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                          pairing: str = "half") -> torch.Tensor:
     """qkv projection, bias, rotary encoding and cache store in one kernel; returns the rotated
     queries [M, n_heads * head_dim] bfloat16.  Same meaning as ``linear`` + ``rope_store``.
     With ``norm_weight``: x is the float32 residual stream and is RMS-normed on the way in."""
     _cuda(x, qkv_weight, bias, positions, inv_freq, slots, k_pages, v_pages, norm_weight)
+    _check_pairing(pairing, "skinny_qkv_rope_store")
     M, K = x.shape
     takes = skinny_norm_takes(x, qkv_weight) if _norm_args(x, norm_weight, "skinny_qkv_rope_store") is not None \
         else skinny_takes(x, qkv_weight)
@@ -532,11 +552,10 @@ def skinny_qkv_rope_store(x: torch.Tensor, qkv_weight: torch.Tensor, bias: Optio
 
 
 # ------------------------------------------------------------------------------------------
-# Products for many tokens on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory).
+# Products for many tokens on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory, two SMs per tile).
 # Measured for gate_up + SwiGLU at 17920 x 1536: the library product followed by the SwiGLU kernel takes 13.8 us at
-# 64 tokens, 15.0 at 128, 17.1 at 200, 18.6 at 256; the pair kernel 17.1 us anywhere up to 256 tokens; the one-SM
-# kernel 22.5 us from 128 to 255.  So the model's feed-forward takes the tcgen05 path from TC_PAIR_MIN_TOKENS = 200
-# tokens on, with the pair kernel; TC_MIN_TOKENS is what the kernels themselves take.
+# 64 tokens, 15.0 at 128, 17.1 at 200, 18.6 at 256; this kernel 17.1 us anywhere up to 256 tokens.  So the model's
+# feed-forward takes the tcgen05 path from TC_PAIR_MIN_TOKENS = 200 tokens on; TC_MIN_TOKENS is what the kernel takes.
 TC_MIN_TOKENS = 128
 
 
@@ -547,33 +566,24 @@ def tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def tc_status() -> int:
-    """0, or 1 when a tcgen05 product kernel gave up waiting on a barrier since the library was loaded."""
-    out, out2 = ctypes.c_int(0), ctypes.c_int(0)
-    library().pico_tc_status(ctypes.addressof(out))
-    library().pico_tp_status(ctypes.addressof(out2))
-    return out.value | out2.value
+    """0, or 1 when the tcgen05 product kernel gave up waiting on a barrier since the library was loaded."""
+    out = ctypes.c_int(0)
+    library().pico_tp_status(ctypes.addressof(out))
+    return out.value
 
 
-TC_PAIR_MIN_TOKENS = 200      # from here on two SMs share a tile (tcgen05.mma.cta_group::2), and the tcgen05 path pays
+TC_PAIR_MIN_TOKENS = 200      # from here on the tcgen05 path pays
 
 
-def _tc_gemm(x, weight, out, residual, M, N, K, epi, pair, what):
-    """One of the two tcgen05 product kernels: a tile per block, or per pair of blocks (``pair``:
-    None = by the number of tokens, True = the pair form with the tile it picks, 256 or 512 = the
-    pair form with that many rows of x per pair)."""
-    if pair is None:
-        pair = M >= TC_PAIR_MIN_TOKENS
-    if pair:
-        rows = 0 if pair is True else int(pair)
-        _check(library().pico_gemm_tcgen05_pair(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), _ptr(residual), M, N, K,
-                                                epi, rows, _stream()), "gemm_tcgen05_pair" + what)
-    else:
-        _check(library().pico_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), _ptr(residual), M, N, K, epi,
-                                           _stream()), "gemm_tcgen05" + what)
+def _tc_gemm(x, weight, out, residual, M, N, K, epi, rows, what):
+    """The tcgen05 product kernel: a tile per pair of blocks (``tcgen05.mma.cta_group::2``).  ``rows``: None = the
+    kernel picks its tile; 256 or 512 = that many rows of x per pair."""
+    _check(library().pico_gemm_tcgen05_pair(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), _ptr(residual), M, N, K,
+                                            epi, int(rows or 0), _stream()), "gemm_tcgen05_pair" + what)
     _count()
 
 
-def tc_linear(x: torch.Tensor, weight: torch.Tensor, pair=None) -> torch.Tensor:
+def tc_linear(x: torch.Tensor, weight: torch.Tensor, rows=None) -> torch.Tensor:
     """x [M, K] times weight[N, K] transposed on the tcgen05 tensor cores; bfloat16 out."""
     _cuda(x, weight)
     if not tc_takes(x, weight):
@@ -581,12 +591,11 @@ def tc_linear(x: torch.Tensor, weight: torch.Tensor, pair=None) -> torch.Tensor:
     M, K = x.shape
     N = weight.shape[0]
     out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-    _tc_gemm(x, weight, out, None, M, N, K, 0, pair, "")
+    _tc_gemm(x, weight, out, None, M, N, K, 0, rows, "")
     return out
 
 
-def tc_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor,
-                       pair=None) -> None:
+def tc_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, rows=None) -> None:
     """residual [M, N] float32 += x [M, K] times weight[N, K] transposed."""
     _cuda(x, weight, residual)
     M, K = x.shape
@@ -594,10 +603,10 @@ def tc_linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Te
     if not tc_takes(x, weight) or residual.dtype != torch.float32 or residual.shape != (M, N) \
             or not residual.is_contiguous():
         raise KernelError("tc_linear_residual: sizes not taken")
-    _tc_gemm(x, weight, None, residual, M, N, K, 1, pair, " (residual)")
+    _tc_gemm(x, weight, None, residual, M, N, K, 1, rows, " (residual)")
 
 
-def tc_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor, pair=None) -> torch.Tensor:
+def tc_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor, rows=None) -> torch.Tensor:
     """silu(x wg^T) * (x wu^T) for gate_up_weight = [wg; wu]; returns [M, I] bfloat16."""
     _cuda(x, gate_up_weight)
     if not tc_takes(x, gate_up_weight):
@@ -605,7 +614,7 @@ def tc_gate_up_swiglu(x: torch.Tensor, gate_up_weight: torch.Tensor, pair=None) 
     M, K = x.shape
     I = gate_up_weight.shape[0] // 2
     out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
-    _tc_gemm(x, gate_up_weight, out, None, M, 2 * I, K, 2, pair, " (swiglu)")
+    _tc_gemm(x, gate_up_weight, out, None, M, 2 * I, K, 2, rows, " (swiglu)")
     return out
 
 

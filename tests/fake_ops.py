@@ -41,7 +41,7 @@ def swiglu(gate_up, out):
 
 
 def rope_store(qkv, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads, head_dim,
-               page_size):
+               page_size, pairing="half"):
     T = qkv.shape[0]
     x = qkv.float()
     if bias is not None:
@@ -153,7 +153,7 @@ def skinny_gate_up_swiglu(x, gate_up_weight, norm_weight=None, eps=0.0):
 
 
 def skinny_qkv_rope_store(x, qkv_weight, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads,
-                          head_dim, page_size, norm_weight=None, eps=0.0):
+                          head_dim, page_size, norm_weight=None, eps=0.0, pairing="half"):
     x = _normed(x, norm_weight, eps)
     qkv = x.float() @ qkv_weight.float().t()          # float32 until after the rotation, like the kernel
     rope_store(qkv, bias, positions, inv_freq, slots, k_pages, v_pages, n_heads, n_kv_heads, head_dim, page_size)

@@ -40,6 +40,11 @@ TINY = {
                        rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
                        max_position_embeddings=2048),
               page_size=32, seed=505),
+    # F: width 2048 (16 query heads on 2 kv heads of 128): wider than the rows the fused norm keeps in registers
+    "f": dict(raw=dict(architectures=["Qwen2ForCausalLM"], vocab_size=350, hidden_size=2048, num_hidden_layers=2,
+                       num_attention_heads=16, num_key_value_heads=2, intermediate_size=384, rope_theta=1000000.0,
+                       rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=2048),
+              page_size=16, seed=606),
 }
 
 
@@ -143,6 +148,27 @@ def trace_mixed(requests, max_live=4, seed=0, chunk_sizes=(5, 17, 2, 9, 33, 3)):
     return steps
 
 
+def trace_many_decoders(requests, tail=6, per_step=8, want_every=3):
+    """Many requests live at once: all but the last ``tail`` tokens of each as whole prompts, ``per_step``
+    requests a step; then ``tail`` steps that hold one token of every request, of which only every
+    ``want_every``-th row (another set each step) is wanted."""
+    rids = list(requests)
+    steps = []
+    for at in range(0, len(rids), per_step):
+        entries = []
+        for rid in rids[at:at + per_step]:
+            head = requests[rid][:-tail]
+            entries.append(dict(id=rid, tokens=head, want=[len(head) - 1]))
+        steps.append(dict(entries=entries, end=[]))
+    for k in range(tail):
+        entries = []
+        for j, rid in enumerate(rids):
+            ids = requests[rid]
+            entries.append(dict(id=rid, tokens=[ids[len(ids) - tail + k]], want=[0] if (j + k) % want_every == 0 else []))
+        steps.append(dict(entries=entries, end=rids if k == tail - 1 else []))
+    return steps
+
+
 def live_token_peak(steps, round_to=64):
     """Most tokens live requests hold at any time, each rounded up to ``round_to``."""
     held, peak = {}, 0
@@ -191,12 +217,12 @@ def replay(runner, steps):
 
 
 def make_runner_from_tensors(name, dtype, device, max_tokens, max_num_seqs=4, use_cuda_graph=False,
-                             poison=True, page_size=None):
+                             poison=True, page_size=None, **options):
     from pico_vllm_b200.config import EngineConfig
     from pico_vllm_b200.engine import ModelRunner, make_cache, model_from_tensors
     cfg = tiny_config(name)
     ecfg = EngineConfig(dtype=dtype, page_size=page_size or TINY[name]["page_size"], max_cache_tokens=max_tokens,
-                        max_num_seqs=max_num_seqs, use_cuda_graph=use_cuda_graph, device=device)
+                        max_num_seqs=max_num_seqs, use_cuda_graph=use_cuda_graph, device=device, **options)
     tensors = tiny_tensors(name, torch.float32 if dtype == "float32" else torch.bfloat16)
     model = model_from_tensors(cfg, tensors, ecfg)
     return ModelRunner(model, make_cache(model, ecfg, poison_freed=poison), ecfg), tensors

@@ -115,17 +115,24 @@ def lm_head(h, w, cfg):
     return h @ w["lm_head.weight"].T
 
 
-def forward(ids, w, cfg, dtype=torch.float32):
-    """Logits [T, vocab] of one whole sequence of token ids (list or 1-D tensor)
-    (pico_vllm/model.py:427-445)."""
+def last_hidden_states(ids, w, cfg, dtype=torch.float32):
+    """The normed states [T, width] that the head multiplies, for one whole sequence of token ids:
+    embedding, every layer, last norm (pico_vllm/model.py:427-444).  For vocabularies so large
+    that logits of every position would not fit, callers apply :func:`lm_head` to the rows they want."""
     ids = torch.as_tensor(ids, dtype=torch.long)
     w = {k: v.to(dtype) for k, v in w.items()}
     positions = torch.arange(ids.shape[0])
     x = embed(ids, w["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, i, positions, cfg)
-    x = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
-    return lm_head(x, w, cfg)
+    return rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+
+
+def forward(ids, w, cfg, dtype=torch.float32):
+    """Logits [T, vocab] of one whole sequence of token ids (list or 1-D tensor)
+    (pico_vllm/model.py:427-445)."""
+    w = {k: v.to(dtype) for k, v in w.items()}
+    return lm_head(last_hidden_states(ids, w, cfg, dtype), w, cfg)
 
 
 def greedy_generate(prompt, w, cfg, n_new, dtype=torch.float32):

@@ -256,3 +256,86 @@ def test_random_workloads_finish_with_every_token_and_no_page_lost():
         run(s)
         assert {r.request_id: len(r.generated_ids) for r in s.finished} == want
         assert all(g.pool.in_use == 0 for g in m.groups)
+
+
+def run_one_step_late(sched, rng, eos_rate=0.0, max_steps=20000):
+    """Drives ``advance`` / ``resolve`` as the engine does one step ahead of the device: a step is
+    scheduled and booked while the tokens of the step before are still unknown, and those are
+    resolved afterwards.  A token is the end token with probability ``eos_rate``."""
+    pending = None
+    for _ in range(max_steps):
+        if not (sched.has_work() or pending):
+            break
+        plan = sched.schedule() if (sched.waiting or sched.running) else []
+        launched = None
+        if plan:
+            assert sum(s.count for s in plan) <= sched.budget
+            slots = [s.request.slot for s in plan]
+            assert len(set(slots)) == len(slots) and None not in slots
+            for s in plan:
+                assert sched.cache.append(s.request.slot, s.count) == s.start
+            for s in plan:
+                sched.cache.commit(s.request.slot)
+            sched.advance(plan)
+            launched = plan
+        else:
+            assert pending is not None, "nothing scheduled and nothing in flight"
+        if pending is not None:
+            toks = [(sched.eos_token_id if rng.random() < eos_rate else 7) for s in pending if s.samples]
+            sched.resolve(pending, toks)
+        pending = launched
+        sched.cache.check()
+    assert not sched.has_work() and pending is None
+
+
+def test_random_workloads_one_step_late_with_end_tokens():
+    """The workloads of the test above through ``advance`` / ``resolve``, with random end tokens: a
+    request whose last token is in flight still holds its pages and slot, which must not be taken
+    for "does not fit even alone"."""
+    rng = random.Random(5)
+    for trial in range(400):
+        m = manager(entries=(FULL, WIN), page_size=4, num_pages=rng.choice([16, 24, 60]), max_num_seqs=rng.choice([2, 4]),
+                    max_seq_len=64)
+        s = Scheduler(m, m.max_num_seqs, rng.choice([8, 16, 64]), prefill_chunk=rng.choice([None, 3, 7]), eos_token_id=0)
+        want = {}
+        for i in range(rng.randint(3, 12)):
+            p, n = rng.randint(1, 40), rng.randint(1, 20)
+            s.add(req(i, p, n, ignore_eos=rng.random() < 0.3))
+            want[i] = n
+        run_one_step_late(s, rng, eos_rate=rng.choice([0.0, 0.1, 0.3]))
+        got = {r.request_id: r for r in s.finished}
+        assert set(got) == set(want)
+        for i, r in got.items():
+            assert all(t >= 0 for t in r.generated_ids)
+            if r.finish_reason == "eos":
+                assert r.generated_ids[-1] == 0 and 0 not in r.generated_ids[:-1] and len(r.generated_ids) <= want[i]
+            else:
+                assert len(r.generated_ids) == want[i]
+        assert all(g.pool.in_use == 0 for g in m.groups) and m.free_slots == m.max_num_seqs
+        assert not s.lingering and not s.draining
+
+
+def test_a_lone_request_that_does_not_fit_still_raises_one_step_late():
+    m = manager(entries=(FULL,), num_pages=3, max_seq_len=400)
+    s = Scheduler(m, 2, 64)
+    s.add(req(0, 20, 30))
+    with pytest.raises(OutOfPages):
+        run_one_step_late(s, random.Random(0))
+
+
+def test_the_cache_length_guard_ends_a_request_that_add_would_have_refused():
+    """``add`` refuses a request whose prompt plus ``max_new_tokens`` exceeds the longest request the cache
+    holds, so a request never meets that limit on its way; the guard in ``finish_step`` / ``advance`` is for
+    requests that reach the waiting line another way.  Put there directly, such a request ends with
+    ``cache_length`` when it fills the cache, in turn and one step late alike."""
+    for late in (False, True):
+        m = manager(entries=(FULL,), num_pages=4, max_seq_len=32)
+        s = Scheduler(m, 2, 64)
+        r = req(0, 28, 10)
+        s.waiting.append(r)                      # not through add()
+        if late:
+            run_one_step_late(s, random.Random(1))
+        else:
+            run(s)
+        assert r.finish_reason == "cache_length" and r.total_len == 32
+        assert all(g.pool.in_use == 0 for g in m.groups)

@@ -56,6 +56,48 @@ def test_every_cutting_matches_plain(dtype, name, cut, graph):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", ["tail", "mixed"])
+def test_a_model_2048_wide(dtype, cut):
+    """Width 2048 (the next larger served shape): at up to 8 tokens the fused norm reads its rows twice instead
+    of keeping them in registers; from 9 tokens on the norm is a kernel of its own."""
+    cfg = helpers.tiny_config("f")
+    reqs = {f"r{i}": helpers.random_ids(n, cfg.vocab_size, 2000 + i) for i, n in enumerate([70, 33, 150, 12, 40, 25])}
+    steps = (helpers.trace_tail_decode(reqs, 12) if cut == "tail"
+             else helpers.trace_many_decoders(reqs, tail=5, per_step=3, want_every=2))
+    runner, tensors = helpers.make_runner_from_tensors("f", dtype, DEV, helpers.live_token_peak(steps), max_num_seqs=8,
+                                                       use_cuda_graph=(cut == "mixed"))
+    want = helpers.expected_logits(steps, reqs, _plain_logits("f", reqs, tensors))
+    for i, (g, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+        if w is not None:
+            helpers.assert_close_logits(g, w, REL[dtype], f"f/{cut}/{dtype} step {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["d", "e"])
+@pytest.mark.parametrize("live", [5, 20, 33, 64])
+@pytest.mark.parametrize("graph", [False, True])
+def test_decode_steps_of_many_live_requests(dtype, name, live, graph):
+    """Decode-only steps of 5 to 64 requests: the graph buckets 8 to 64 (padded), the products for more than
+    16 tokens in a decode step, fewer splits of the key range as the batch grows, and logits of only some rows."""
+    cfg = helpers.tiny_config(name)
+    reqs = {f"r{i}": helpers.random_ids(9 + (i * 7) % 45, cfg.vocab_size, 300 + i) for i in range(live)}
+    steps = helpers.trace_many_decoders(reqs)
+    runner, tensors = helpers.make_runner_from_tensors(name, dtype, DEV, helpers.live_token_peak(steps),
+                                                       max_num_seqs=64, use_cuda_graph=graph,
+                                                       max_num_batched_tokens=4096)
+    want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
+    got = helpers.replay(runner, steps)
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert (g is None) == (w is None)
+        if w is not None:
+            assert g.shape == w.shape
+            helpers.assert_close_logits(g, w, REL[dtype], f"{name}/{dtype}/{live} live step {i}")
+    if graph:
+        assert runner.graph_replays == 6
+    assert all(g.pool.in_use == 0 for g in runner.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["a", "b", "d"])
 def test_long_decoding(dtype, name):
     """A short prompt, then 400 tokens one by one (pages fill up, the window moves on)."""
@@ -176,13 +218,49 @@ def test_a_folder_stored_in_32_bit_served_in_bfloat16(tmp_path):
 
 def test_command_line_generates(tmp_path, capsys):
     from pico_vllm_b200.cli import main
-    helpers.write_tiny_model("a", tmp_path, dtype="bfloat16")
-    rc = main(["run", "--model", str(tmp_path), "--prompt-ids", "5,17,3", "--prompt-ids", "9,9", "--max-new-tokens", "4",
-               "--temperature", "0", "--num-gpu-blocks", "32", "--ignore-eos"])
+    helpers.write_tiny_model("a", tmp_path, dtype="float32")
+    prompts = [[5, 17, 3], [9, 9]]
+    rc = main(["run", "--model", str(tmp_path), "--dtype", "float32", "--prompt-ids", "5,17,3", "--prompt-ids", "9,9",
+               "--max-new-tokens", "4", "--temperature", "0", "--num-gpu-blocks", "32", "--ignore-eos"])
     assert rc == 0
     lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("[")]
     assert len(lines) == 2
-    assert sorted(len(l.split("] ")[1].split()) for l in lines) == [2 + 4, 3 + 4]
+    printed = {int(l[1:l.index("]")]): [int(t) for t in l.split("] ")[1].split()] for l in lines}
+    tensors = helpers.tiny_tensors("a", torch.float32)
+    pcfg = helpers.plain_config(helpers.tiny_config("a"))
+    for rid, p in enumerate(prompts):       # the reference prints prompt and generated tokens together
+        assert printed[rid] == p + plain.greedy_generate(p, tensors, pcfg, 4)
+
+
+@pytest.mark.parametrize("ahead", [True, False])
+def test_generation_with_preemption_and_end_tokens(ahead, tmp_path):
+    """So few pages that requests are pre-empted and recomputed, and an end token that some requests
+    meet, one step ahead of the device and in turn: a request that was pre-empted, or that ended, while
+    a step of its own was in flight must neither lose nor keep a token, and every page comes back."""
+    from pico_vllm_b200 import LLM, SamplingParams
+    name = "b"
+    cfg = helpers.tiny_config(name)
+    helpers.write_tiny_model(name, tmp_path, dtype="float32")
+    tensors = helpers.tiny_tensors(name, torch.float32)
+    pcfg = helpers.plain_config(cfg)
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 50 + n) for n in (1, 9, 24, 40, 13, 30, 6, 21, 35)]
+    want = [plain.greedy_generate(p, tensors, pcfg, 10) for p in prompts]
+    eos = want[3][4]                       # request 3 meets it as its 5th token; others may meet it too
+    llm = LLM(str(tmp_path), dtype="float32", device=DEV, page_size=8, num_pages=14, max_num_seqs=4,
+              max_num_batched_tokens=16, prefill_chunk=7, max_model_len=112, async_scheduling=ahead)
+    llm.scheduler.eos_token_id = eos
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=10))
+    hit = 0
+    for w, o in zip(want, outs):
+        cut = w.index(eos) + 1 if eos in w else len(w)
+        assert o.token_ids == w[:cut]
+        assert o.finish_reason == ("eos" if eos in w else "length")
+        hit += eos in w
+    assert hit >= 1 and llm.scheduler.num_preemptions > 0
+    llm.cache.check()
+    assert all(g.pool.in_use == 0 for g in llm.cache.groups) and llm.cache.free_slots == llm.cache.max_num_seqs
+    from pico_vllm_b200 import ops
+    ops.check_kernel_status()
 
 
 def test_sampling_through_the_entry_point_is_reproducible(tmp_path):

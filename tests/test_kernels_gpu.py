@@ -372,9 +372,11 @@ def test_skinny_qkv_rope_store(M, nh, nkv, hd, ps, rot, K):
 
 
 @pytest.mark.parametrize("M", [1, 8, 11, 16])
-@pytest.mark.parametrize("K,eps", [(64, 1e-6), (1536, 1e-6), (192, 1e-5), (80, 1e-3)])
+@pytest.mark.parametrize("K,eps", [(64, 1e-6), (1536, 1e-6), (192, 1e-5), (80, 1e-3), (2048, 1e-6), (2096, 1e-5)])
 def test_skinny_kernels_with_the_norm_inside(M, K, eps):
-    """The residual stream goes in as float32 and is RMS-normed inside the product kernels."""
+    """The residual stream goes in as float32 and is RMS-normed inside the product kernels.  Rows up to
+    1536 wide are kept in registers between the two passes of the norm; wider rows (2048, 2096: taken at up
+    to 8 tokens) are read twice."""
     from pico_vllm_b200 import ops
     T = M + 3
     x = torch.randn(T, K, generator=gen(80)) * 2
@@ -413,32 +415,32 @@ def test_skinny_kernels_with_the_norm_inside(M, K, eps):
     assert torch.allclose(kg.cpu().float(), kr.float(), **t) and torch.allclose(vg.cpu().float(), vr.float(), **t)
 
 
-@pytest.mark.parametrize("pair", [False, True, 512])
+@pytest.mark.parametrize("rows", [None, 256, 512])
 @pytest.mark.parametrize("M", [128, 200, 2048, 777])
 @pytest.mark.parametrize("N,K", [(256, 64), (2048, 1536), (1536, 1536), (1536, 8960), (272, 200), (512, 192)])
-def test_tcgen05_linear_store_and_residual(M, N, K, pair):
+def test_tcgen05_linear_store_and_residual(M, N, K, rows):
     from pico_vllm_b200 import ops
     x = torch.randn(M, K, generator=gen(90)).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=gen(91)) / math.sqrt(K)).to(torch.bfloat16)
     want = x.float() @ w.float().t()
-    got = ops.tc_linear(x.to(DEV), w.to(DEV), pair=pair).cpu().float()
+    got = ops.tc_linear(x.to(DEV), w.to(DEV), rows=rows).cpu().float()
     assert torch.allclose(got, want, atol=3e-2, rtol=2e-2)
     res = torch.randn(M, N, generator=gen(92))
     rg = res.to(DEV)
-    ops.tc_linear_residual(x.to(DEV), w.to(DEV), rg, pair=pair)
+    ops.tc_linear_residual(x.to(DEV), w.to(DEV), rg, rows=rows)
     assert torch.allclose(rg.cpu(), res + want, atol=5e-3, rtol=5e-3)
     torch.cuda.synchronize()
     assert ops.tc_status() == 0
 
 
-@pytest.mark.parametrize("pair", [False, True, 512])
+@pytest.mark.parametrize("rows", [None, 256, 512])
 @pytest.mark.parametrize("M", [128, 333, 2048])
 @pytest.mark.parametrize("I,K", [(128, 64), (8960, 1536), (320, 192), (176, 80)])
-def test_tcgen05_gate_up_swiglu(M, I, K, pair):
+def test_tcgen05_gate_up_swiglu(M, I, K, rows):
     from pico_vllm_b200 import ops
     x = torch.randn(M, K, generator=gen(93)).to(torch.bfloat16)
     w = (torch.randn(2 * I, K, generator=gen(94)) * 2 / math.sqrt(K)).to(torch.bfloat16)
-    got = ops.tc_gate_up_swiglu(x.to(DEV), w.to(DEV), pair=pair).cpu().float()
+    got = ops.tc_gate_up_swiglu(x.to(DEV), w.to(DEV), rows=rows).cpu().float()
     want = fake_ops.skinny_gate_up_swiglu(x, w).float()
     assert torch.allclose(got, want, atol=3e-2, rtol=3e-2)
     torch.cuda.synchronize()

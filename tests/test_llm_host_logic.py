@@ -94,3 +94,22 @@ def test_end_token_stops_a_request_and_frees_its_pages(monkeypatch, tmp_path, ah
     # the engine can go on after that
     again = llm.generate(prompts[:1], SamplingParams(temperature=0.0, max_new_tokens=10, ignore_eos=True))
     assert again[0].token_ids == want[0]
+
+
+@pytest.mark.parametrize("ahead", [True, False])
+def test_pages_held_by_a_request_in_flight_are_waited_for(monkeypatch, tmp_path, ahead):
+    """4 pages: a request that fills 3 of them and generates a page's worth of tokens, then a
+    short one.  One step ahead of the device, the first request's last token is still in flight
+    (and its pages are still held) when the second is scheduled: the scheduler must wait for that
+    step instead of reporting that the second request does not fit even alone."""
+    from pico_vllm_b200 import SamplingParams
+    ps = helpers.TINY["a"]["page_size"]
+    llm = _llm(monkeypatch, tmp_path, "a", num_pages=4, max_num_seqs=2, async_scheduling=ahead)
+    cfg = helpers.tiny_config("a")
+    prompts = [helpers.random_ids(3 * ps, cfg.vocab_size, 1), helpers.random_ids(ps + 3, cfg.vocab_size, 2)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=ps, ignore_eos=True))
+    tensors = helpers.tiny_tensors("a", torch.float32)
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain.greedy_generate(p, tensors, helpers.plain_config(cfg), ps)
+    llm.cache.check()
+    assert all(g.pool.in_use == 0 for g in llm.cache.groups)

@@ -70,6 +70,17 @@ def _call_ordinary(c, splits):
     return out
 
 
+def _plain(c):
+    """The same attention by the plain double of the kernels, on the CPU."""
+    import fake_ops
+    T = c["q"].shape[0]
+    out = torch.empty(T, c["nh"] * c["hd"], dtype=c["q"].dtype)
+    fake_ops.paged_attention(c["q"].cpu(), c["k"].cpu(), c["v"].cpu(), out, c["seg"].cpu(), c["pos"].cpu(),
+                             c["table"].cpu(), c["nh"], c["nkv"], c["hd"], c["ps"], c["window"],
+                             1.0 / math.sqrt(c["hd"]))
+    return out
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row(dtype):
     fn = _entry()
@@ -82,6 +93,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row(dtype):
         want = _call_ordinary(c, splits)
         torch.cuda.synchronize()
         assert torch.allclose(got.float(), want.float(), **tol)
+        assert torch.allclose(got.float().cpu(), _plain(c).float(), **tol)      # and the plain attention, directly
 
 
 def test_no_alloc_entry_point_refuses_more_scratch_than_it_has():
@@ -90,3 +102,17 @@ def test_no_alloc_entry_point_refuses_more_scratch_than_it_has():
     rc, _, msg = _call_noalloc(fn, c, 64)        # 64 * 32 * 64 * 130 floats > 2 Mi
     assert rc == -5
     assert "scratch" in msg and "2097152" in msg
+
+
+def test_no_alloc_entry_point_takes_any_number_of_tokens_with_one_part():
+    """With one part per token the kernels use no scratch, so the limit does not apply: 2,048 tokens of 12
+    heads of 128 would need 3.2 Mi floats per part if they did."""
+    fn = _entry()
+    c = _case(4, torch.bfloat16, nh=12, nkv=2, hd=128, lens=tuple([37] * 2048))
+    rc, got, msg = _call_noalloc(fn, c, 1)
+    assert rc == 0, msg
+    want = _call_ordinary(c, 1)
+    torch.cuda.synchronize()
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    rc, _, msg = _call_noalloc(fn, c, 2)
+    assert rc == -5 and "scratch" in msg
