@@ -38,6 +38,7 @@ class KVGroup:
     pool: PagePool
     tables: np.ndarray                 # int32 [max_num_seqs, max_blocks]; -1 = no page
     first_block: np.ndarray            # int32 [max_num_seqs]; blocks below were given back
+    end_block: np.ndarray              # int32 [max_num_seqs]; blocks first_block .. end_block-1 hold pages
     tensors: Dict[str, torch.Tensor] = field(default_factory=dict)   # name -> [len(entries), num_pages, *page shape]
 
     @property
@@ -74,7 +75,7 @@ class CacheManager:
                     self.entry_group[eid] = (len(self.groups), 0)
                     self.groups.append(KVGroup(spec, [eid], PagePool(num_pages),
                                                np.full((max_num_seqs, self.max_blocks), -1, np.int32),
-                                               np.zeros(max_num_seqs, np.int32)))
+                                               np.zeros(max_num_seqs, np.int32), np.zeros(max_num_seqs, np.int32)))
             else:
                 self.state_specs[eid] = spec
         if allocate:
@@ -111,6 +112,7 @@ class CacheManager:
         self.pending[slot] = 0
         for g in self.groups:
             g.first_block[slot] = 0
+            g.end_block[slot] = 0
         for st in self.states.values():
             st[slot].zero_()
         return slot
@@ -124,6 +126,7 @@ class CacheManager:
             held = row[row >= 0].tolist()
             self._give_back(g, held)
             row[:] = -1
+            g.end_block[slot] = 0
         self.owner[slot] = None
         self.seq_len[slot] = 0
         self.pending[slot] = 0
@@ -138,10 +141,8 @@ class CacheManager:
 
     # ------------------------------------------------------------------ pages for new tokens
     def _blocks_missing(self, g: KVGroup, slot: int, new_len: int) -> int:
-        need = -(-new_len // self.page_size)
-        row = g.tables[slot]
-        have = int(g.first_block[slot]) + int(np.count_nonzero(row[g.first_block[slot]:need] >= 0))
-        return max(0, need - have)
+        # pages are taken block after block, so the blocks that hold pages are first_block .. end_block - 1
+        return max(0, -(-new_len // self.page_size) - int(g.end_block[slot]))
 
     def pages_needed(self, slot: int, n_new: int) -> List[int]:
         """Pages each group would have to take to hold n_new more tokens of this request."""
@@ -172,13 +173,9 @@ class CacheManager:
                 raise OutOfPages(f"{n} pages wanted for {n_new} tokens, {g.pool.available} of {g.pool.num_pages} free")
         for n, g in zip(need, self.groups):
             if n:
-                pages = g.pool.allocate(n)
-                row = g.tables[slot]
-                last = -(-new_len // self.page_size)
-                empty = [b for b in range(int(g.first_block[slot]), last) if row[b] < 0]
-                assert len(empty) == n, (empty, n)
-                for b, p in zip(empty, pages):
-                    row[b] = p
+                end = int(g.end_block[slot])
+                g.tables[slot, end:end + n] = g.pool.allocate(n)
+                g.end_block[slot] = end + n
         self.pending[slot] += n_new
         return start
 
@@ -213,6 +210,14 @@ class CacheManager:
         if (pages < 0).any():
             raise PicoError(f"slot {slot}: positions {start}..{start + n - 1} have no page")
         return (pages * self.page_size + pos % self.page_size).astype(np.int32)
+
+    def slot_mapping_single(self, group: int, slots: np.ndarray, positions: np.ndarray) -> np.ndarray:
+        """The same for one position of each of many requests (a decode step), without a loop."""
+        pages = self.groups[group].tables[slots, positions // self.page_size].astype(np.int64)
+        if (pages < 0).any():
+            bad = int(slots[np.argmax(pages < 0)])
+            raise PicoError(f"slot {bad}: its next position has no page")
+        return (pages * self.page_size + positions % self.page_size).astype(np.int32)
 
     def table_row(self, group: int, slot: int) -> np.ndarray:
         return self.groups[group].tables[slot]

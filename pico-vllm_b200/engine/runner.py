@@ -240,19 +240,29 @@ class ModelRunner:
         cu = h[lay.cu_q:lay.cu_q + S + 1]
         ss = h[lay.seg_slots:lay.seg_slots + S]
         ss[:] = 0
-        at = 0
-        for i, (it, n, st) in enumerate(zip(items, q_lens, starts)):
-            tok[at:at + n] = np.asarray(it.tokens, dtype=np.int32)
-            pos[at:at + n] = np.arange(st, st + n, dtype=np.int32)
-            seg[at:at + n] = i
-            cu[i] = at
-            ss[i] = it.slot
-            at += n
-        for i in range(S_real, S):      # padding segments of one token each
-            seg[at] = i
-            cu[i] = at
-            at += 1
-        cu[S] = at
+        single = T_real == S_real       # every segment is one token: no loop over the items
+        if single:
+            slot_ids = np.fromiter((it.slot for it in items), dtype=np.int64, count=S_real)
+            start_pos = np.asarray(starts, dtype=np.int64)
+            tok[:S_real] = np.fromiter((it.tokens[0] for it in items), dtype=np.int64, count=S_real)
+            pos[:S_real] = start_pos
+            seg[:] = np.arange(T, dtype=np.int32)
+            cu[:] = np.arange(S + 1, dtype=np.int32)
+            ss[:S_real] = slot_ids
+        else:
+            at = 0
+            for i, (it, n, st) in enumerate(zip(items, q_lens, starts)):
+                tok[at:at + n] = np.asarray(it.tokens, dtype=np.int32)
+                pos[at:at + n] = np.arange(st, st + n, dtype=np.int32)
+                seg[at:at + n] = i
+                cu[i] = at
+                ss[i] = it.slot
+                at += n
+            for i in range(S_real, S):      # padding segments of one token each
+                seg[at] = i
+                cu[i] = at
+                at += 1
+            cu[S] = at
         pf = [i for i, n in enumerate(q_lens) if n > 1]
         dec = [int(cu[i]) for i, n in enumerate(q_lens) if n == 1] + list(range(T_real, T))
         h[lay.prefill_segs:lay.prefill_segs + len(pf)] = np.asarray(pf, dtype=np.int32)
@@ -265,6 +275,10 @@ class ModelRunner:
             sl[:] = -1
             tb = h[lay.g_tables[gi]:lay.g_tables[gi] + S * W].reshape(S, W)
             tb[:] = 0
+            if single:
+                sl[:S_real] = cache.slot_mapping_single(gi, slot_ids, start_pos)
+                tb[:S_real] = np.maximum(g.tables[slot_ids, :W], 0)
+                continue
             at = 0
             for i, (it, n, st) in enumerate(zip(items, q_lens, starts)):
                 sl[at:at + n] = cache.slot_mapping(gi, it.slot, st, n)
