@@ -16,6 +16,10 @@
 //   SWIGLU    a[m, i] = silu(gate_i) * up_i; rows i (gate) and I + i (up)   (gate_up, no 2I buffer)
 //   ROPE      q/k heads: rows d and d + hd/2 of a head: bias, rotation by the token's position,
 //             q to the query buffer, k and v straight into their cache pages   (qkv projection)
+//   ARGMAX    token[m] = the first n with the largest sum: every block keeps the best of its own tiles, the
+//             block that finishes last picks among the blocks' bests (greedy head: the [M, N] logits are
+//             never written; the reference computes them all and calls argmax, pico_vllm/model.py:445,
+//             pico_vllm/sampler.py:3-8)
 //
 // The reference runs these as cuBLAS nn.Linear calls followed by separate kernels
 // (pico_vllm/model.py:200-225, 290-295, 326-332; pico_vllm/kernels/swiglu.py,
@@ -46,7 +50,14 @@
 #define SG_CTAS_PER_SM 2
 #endif
 
-enum { SG_STORE = 0, SG_RESIDUAL = 1, SG_SWIGLU = 2, SG_ROPE = 3 };
+enum { SG_STORE = 0, SG_RESIDUAL = 1, SG_SWIGLU = 2, SG_ROPE = 3, SG_ARGMAX = 4 };
+
+// ARGMAX: what each block found, and how many blocks have reported (reset by the block that reports last, so
+// launches on one stream need no clearing in between; launches that overlap on the GPU would mix their entries)
+#define SG_ARGMAX_MAX_GRID 1024
+__device__ float g_sg_best_v[SG_ARGMAX_MAX_GRID * 16];
+__device__ int g_sg_best_i[SG_ARGMAX_MAX_GRID * 16];
+__device__ unsigned int g_sg_reported = 0;
 
 struct SkinnyArgs {
     const bf16* w;            // [N, K]
@@ -75,6 +86,8 @@ struct SkinnyArgs {
     bf16* q_out;              // [M, nh * hd]
     bf16* k_pages;
     bf16* v_pages;
+    // ARGMAX
+    int* tokens;              // [M]
 };
 
 __device__ __forceinline__ uint32_t sg_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -129,9 +142,25 @@ __device__ __forceinline__ float sg_sum(const float* red, int f, int t) {
 }
 
 template <int MT, int EPI>
-__device__ __forceinline__ void sg_epilogue(const SkinnyArgs& p, const float* red, int row_a, int row_b) {
+__device__ __forceinline__ void sg_epilogue(const SkinnyArgs& p, const float* red, int row_a, int row_b, float* best_v,
+                                            int* best_i) {
     constexpr int XR = MT * 8;
-    if (EPI == SG_STORE || EPI == SG_RESIDUAL) {
+    if (EPI == SG_ARGMAX) {
+        // one thread per token: the tile's 16 features in rising order of n, so that the first of equals wins
+        const int t = threadIdx.x;
+        if (t < p.M) {
+            float bv = best_v[t];
+            int bi = best_i[t];
+#pragma unroll
+            for (int f = 0; f < 16; ++f) {
+                const float v = sg_sum<XR>(red, f, t);
+                const int n = (f < 8 ? row_a + f : row_b + f - 8);
+                if (v > bv || (v == bv && n < bi)) { bv = v; bi = n; }
+            }
+            best_v[t] = bv;
+            best_i[t] = bi;
+        }
+    } else if (EPI == SG_STORE || EPI == SG_RESIDUAL) {
         for (int idx = threadIdx.x; idx < 16 * XR; idx += SG_THREADS) {
             const int t = idx / 16, f = idx - t * 16;          // consecutive threads: consecutive features
             if (t >= p.M) continue;
@@ -215,6 +244,12 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
     bf16* ring = reinterpret_cast<bf16*>(sg_smem) + (size_t)warp * STAGES * STAGE_ELEMS;
     bf16* x_all = reinterpret_cast<bf16*>(sg_smem) + (size_t)SG_WARPS * STAGES * STAGE_ELEMS;     // XPRE: [XR][x_ld]
     float* red = reinterpret_cast<float*>(x_all + (XPRE ? (size_t)XR * x_ld : 0));          // [warps][16][XR]
+    float* best_v = red + SG_WARPS * 16 * XR;                                                // ARGMAX: [XR], [XR]
+    int* best_i = reinterpret_cast<int*>(best_v + XR);
+    if (EPI == SG_ARGMAX && threadIdx.x < XR) {
+        best_v[threadIdx.x] = -INFINITY;
+        best_i[threadIdx.x] = 0x7fffffff;
+    }
     const int nk64 = (p.K + SG_KW - 1) / SG_KW;
     const int nkw = nk64 > warp ? (nk64 - warp + SG_WARPS - 1) / SG_WARPS : 0;     // 64-wide slices of K this warp takes per tile
     const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -398,10 +433,43 @@ __global__ void __launch_bounds__(SG_THREADS) skinny_gemm_kernel(const SkinnyArg
             }
         }
         __syncthreads();
-        sg_epilogue<MT, EPI>(p, red, row_a, row_b);
+        sg_epilogue<MT, EPI>(p, red, row_a, row_b, best_v, best_i);
         __syncthreads();         // red is written again at the end of the next tile
     }
     sg_wait<0>();
+    if (EPI == SG_ARGMAX) {
+        // this block's bests go to its row of the global table; the block that reports last reads all rows
+        __shared__ unsigned int ticket;
+        if (threadIdx.x < XR) {
+            g_sg_best_v[blockIdx.x * 16 + threadIdx.x] = best_v[threadIdx.x];
+            g_sg_best_i[blockIdx.x * 16 + threadIdx.x] = best_i[threadIdx.x];
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) ticket = atomicAdd(&g_sg_reported, 1u);
+        __syncthreads();
+        if (ticket == gridDim.x - 1) {
+            __threadfence();
+            // a warp per token: lanes take blocks lane, lane + 32, ...; the smaller index wins among equals
+            for (int t = warp; t < p.M; t += SG_WARPS) {
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                for (int b = lane; b < (int)gridDim.x; b += 32) {
+                    const float v = __ldcg(&g_sg_best_v[b * 16 + t]);
+                    const int n = __ldcg(&g_sg_best_i[b * 16 + t]);
+                    if (v > bv || (v == bv && n < bi)) { bv = v; bi = n; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float v = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int n = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (v > bv || (v == bv && n < bi)) { bv = v; bi = n; }
+                }
+                if (lane == 0) p.tokens[t] = bi == 0x7fffffff ? 0 : bi;
+            }
+            if (threadIdx.x == 0) g_sg_reported = 0;
+        }
+    }
 }
 
 // Do the activations of all of K fit in shared memory beside the weight rings (two blocks per SM)?
@@ -413,7 +481,8 @@ template <int MT, int EPI, int STAGES, bool XPRE>
 static void sg_launch_one(const SkinnyArgs& a, int tiles, int grid, cudaStream_t stream) {
     const int x_ld = ((a.K + SG_KW - 1) / SG_KW) * SG_KW + 8;
     const size_t smem = (size_t)SG_WARPS * STAGES * (XPRE ? 16 : 16 + MT * 8) * SG_LD * sizeof(bf16) +
-                        (XPRE ? (size_t)MT * 8 * x_ld * sizeof(bf16) : 0) + (size_t)SG_WARPS * 16 * MT * 8 * sizeof(float);
+                        (XPRE ? (size_t)MT * 8 * x_ld * sizeof(bf16) : 0) + (size_t)SG_WARPS * 16 * MT * 8 * sizeof(float) +
+                        (EPI == SG_ARGMAX ? (size_t)2 * MT * 8 * sizeof(float) : 0);
     cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI, STAGES, XPRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     pico_launch((skinny_gemm_kernel<MT, EPI, STAGES, XPRE>), dim3(grid), dim3(SG_THREADS), smem, stream, a, tiles, x_ld);
 }
@@ -423,7 +492,8 @@ static int sg_launch(const SkinnyArgs& a, int tiles, cudaStream_t stream) {
     const int mt = (a.M + 7) / 8;
     const int sms = sg_num_sms();
     // persistent blocks, SG_CTAS_PER_SM per SM
-    const int grid = tiles < SG_CTAS_PER_SM * sms ? tiles : SG_CTAS_PER_SM * sms;
+    int grid = tiles < SG_CTAS_PER_SM * sms ? tiles : SG_CTAS_PER_SM * sms;
+    if (EPI == SG_ARGMAX && grid > SG_ARGMAX_MAX_GRID) grid = SG_ARGMAX_MAX_GRID;
     // the activations of all of K stay in shared memory when they fit beside the weight rings
     const bool xpre = sg_xpre(mt, a.K);
     if (a.xf && !xpre) return PICO_ERR_SIZE;
@@ -512,4 +582,15 @@ PICO_API int pico_skinny_qkv_rope_store(const void* x, int ldx, const void* w, c
     a.positions = positions; a.slots = slots; a.inv_freq = inv_freq;
     a.q_out = (bf16*)q_out; a.k_pages = (bf16*)k_pages; a.v_pages = (bf16*)v_pages;
     return sg_launch<SG_ROPE>(a, N / 16, stream);
+}
+
+// tokens[m] = the first n that maximises (x w^T)[m, n]: the greedy choice of the head without the logits.
+// With norm_w: x is the float32 residual stream [*, K] (rows x_rows[m] or m), RMS-normed on the way in.  N % 16 == 0.
+// Its launches must follow one another on one stream (they share the table of the blocks' bests).
+PICO_API int pico_skinny_argmax(const void* x, int ldx, const void* w, int* tokens, int M, int N, int K, const float* norm_w,
+                                float eps, const int* x_rows, cudaStream_t stream) {
+    if (sg_check(M, N, K, norm_w ? 8 : ldx) || N % 16 != 0 || !tokens) return PICO_ERR_SIZE;
+    SkinnyArgs a = {};
+    a.w = (const bf16*)w; sg_set_x(a, x, ldx, norm_w, eps, x_rows); a.M = M; a.N = N; a.K = K; a.tokens = tokens;
+    return sg_launch<SG_ARGMAX>(a, N / 16, stream);
 }

@@ -47,6 +47,9 @@ class Batch:
     num_decode_tokens: int = 0
     # tokens chosen by the sampling kernel in the step before; a token id -(j+1) in token_ids means feedback[j]
     feedback: Optional[torch.Tensor] = None
+    # int32, one entry per wanted row: when given, the head may write the greedy token of every wanted row here and
+    # return no logits
+    greedy_out: Optional[torch.Tensor] = None
 
     def plan(self, mixer):
         """The plan ``mixer.plan(shape)`` returned for this step, or None."""

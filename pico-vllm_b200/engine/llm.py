@@ -139,7 +139,10 @@ class LLM:
         if not plan:
             return []
         logits, rows = self._launch(plan)
-        toks = self.sampler.sample(logits, *self._sampling_args(rows))
+        if logits is None:          # every row greedy and chosen inside the head's kernel
+            toks = self.sampler.tokens_from(self.runner.feedback, len(rows)).result()
+        else:
+            toks = self.sampler.sample(logits, *self._sampling_args(rows))
         it = iter(toks)
         sampled = [next(it) if s.samples else None for s in plan]
         self.stats["steps"] += 1
@@ -153,7 +156,10 @@ class LLM:
         launched = None
         if plan:
             logits, rows = self._launch(plan)
-            handle = self.sampler.sample_async(logits, *self._sampling_args(rows), out=self.runner.feedback)
+            if logits is None:      # every row greedy and chosen inside the head's kernel: the tokens are in feedback
+                handle = self.sampler.tokens_from(self.runner.feedback, len(rows))
+            else:
+                handle = self.sampler.sample_async(logits, *self._sampling_args(rows), out=self.runner.feedback)
             self.scheduler.advance(plan)
             launched = (plan, handle)
             self.stats["steps"] += 1
@@ -170,8 +176,10 @@ class LLM:
             toks = s.request.all_ids[s.start:s.start + s.count]
             items.append(StepItem(s.request.slot, toks, (s.count - 1,) if s.samples else ()))
             self.stats["decode_tokens" if s.request.is_decoding else "prefill_tokens"] += s.count
-        logits = self.runner.step(items)
-        return logits, [s for s in plan if s.samples]
+        rows = [s for s in plan if s.samples]
+        greedy = bool(rows) and all(r.request.temperature <= 0 for r in rows)
+        logits = self.runner.step(items, greedy=greedy)
+        return logits, rows
 
     def _sampling_args(self, rows):
         seeds = [(r.request.seed if r.request.seed is not None else self.cfg.seed) for r in rows]

@@ -86,7 +86,7 @@ class ModelRunner:
         self.device = cache.device
         self.on_gpu = self.device.type == "cuda"
         self.views = cache.views()
-        # ("decode", bucket, plans' key) or ("prefill", tokens, wanted rows, plans' key) -> recorded step
+        # ("decode", bucket, plans' key, greedy) or ("prefill", tokens, wanted rows, plans' key, greedy) -> recorded step
         self._graphs: dict = {}
         g = cfg.graph_prefill_tokens
         if g is None:
@@ -138,10 +138,15 @@ class ModelRunner:
         return self._scratch
 
     # ------------------------------------------------------------------ the step
-    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+    def step(self, items: Sequence[StepItem], greedy: bool = False) -> Optional[torch.Tensor]:
         """Runs the items as one batch; returns float32 logits [wanted, vocab] on the device, in
         the order of the items and of each item's ``want``.  The result of a graph-replayed step
-        lives in a buffer that the next such step overwrites."""
+        lives in a buffer that the next such step overwrites.
+
+        ``greedy``: the caller only wants the most likely token of every wanted row.  Where the head
+        can find it inside its own kernel, the tokens are left in ``self.feedback`` (int32, one per
+        wanted row, in order), no logits are written and None is returned; otherwise logits come back
+        as usual and the caller chooses."""
         if not items:
             return torch.empty((0, self.model.vocab_size), dtype=torch.float32, device=self.device)
         V = self.model.vocab_size
@@ -183,12 +188,12 @@ class ModelRunner:
         try:
             if (decode_only and self.cfg.use_cuda_graph and self.on_gpu
                     and len(items) <= max(self.cfg.graph_batch_sizes)):
-                logits = self._step_graph(items, starts)
+                logits = self._step_graph(items, starts, greedy)
             elif (len(items) == 1 and len(items[0].tokens) == self._graph_prefill_tokens and len(items[0].want) <= 1
                     and self.cfg.use_cuda_graph and self.on_gpu):
-                logits = self._step_prefill_graph(items, starts)
+                logits = self._step_prefill_graph(items, starts, greedy)
             else:
-                batch = self._build(items, starts, pad_to=None)
+                batch = self._build(items, starts, pad_to=None, greedy=greedy)
                 logits = self.model.forward(batch, self.views)
         except Exception:
             for it in items:
@@ -200,7 +205,7 @@ class ModelRunner:
         return logits
 
     def _build(self, items: Sequence[StepItem], starts: List[int], pad_to: Optional[int],
-               buffers=None, scratch=None, rows: Optional[int] = None, plans=None) -> Batch:
+               buffers=None, scratch=None, rows: Optional[int] = None, plans=None, greedy: bool = False) -> Batch:
         """Index arrays of the step on the device.  ``pad_to``: number of one-token segments of
         a graph bucket (the batch is padded to it and the block tables keep their full width);
         ``buffers``/``scratch``/``plans``: a recorded shape's own staging and scratch tensors, which must
@@ -302,59 +307,68 @@ class ModelRunner:
                      prefill_segs=d(lay.prefill_segs, len(pf)) if len(pf) < S else None, num_prefill_segs=len(pf),
                      max_prefill_q=max([q_lens[i] for i in pf], default=0),
                      decode_tokens=d(lay.decode_tokens, len(dec)) if len(dec) < T else None,
-                     num_decode_tokens=len(dec), feedback=self.feedback)
+                     num_decode_tokens=len(dec), feedback=self.feedback,
+                     greedy_out=self.feedback if greedy and R > 0 else None)
 
     # ------------------------------------------------------------------ CUDA graph replay of decode steps
     def _bucket(self, n: int) -> int:
         return min(b for b in self.cfg.graph_batch_sizes if b >= n)
 
-    def _step_graph(self, items: Sequence[StepItem], starts: List[int]) -> torch.Tensor:
+    def _step_graph(self, items: Sequence[StepItem], starts: List[int], greedy: bool = False) -> Optional[torch.Tensor]:
         B = self._bucket(len(items))
-        # every segment has one token; logits are computed for every row of the bucket
+        # every segment has one token; logits (or greedy tokens) are computed for every row of the bucket
         full = [StepItem(it.slot, it.tokens, (0,)) for it in items]
+        rows = [i for i, it in enumerate(items) if len(it.want)]
+        greedy = greedy and len(rows) == len(items)        # tokens land in row order: only when every row is wanted
         # a recorded step holds for one set of plans: as contexts grow a bucket may be recorded a few times
         # (for attention: once per number of splits of the key range)
         plans, plan_key, need = self._plan([1] * len(items), starts, B, B)
-        entry = self._graphs.get(("decode", B, plan_key))
+        key = ("decode", B, plan_key, greedy)
+        entry = self._graphs.get(key)
         if entry is None:
-            logits = self._record(("decode", B, plan_key), full, starts, B, B, plans, need)
+            logits = self._record(key, full, starts, B, B, plans, need, greedy)
         else:
-            self._build(full, starts, pad_to=B, buffers=entry["buffers"], scratch=entry["scratch"], plans=entry["plans"])
+            self._build(full, starts, pad_to=B, buffers=entry["buffers"], scratch=entry["scratch"], plans=entry["plans"],
+                        greedy=greedy)
             entry["graph"].replay()
             ops._count(entry["launches"])
             logits = entry["logits"]
         self.graph_replays += 1
-        rows = [i for i, it in enumerate(items) if len(it.want)]
+        if logits is None:
+            return None
         if len(rows) == len(items):
             return logits[:len(items)]
         return logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else logits[:0]
 
-    def _step_prefill_graph(self, items: Sequence[StepItem], starts: List[int]) -> torch.Tensor:
+    def _step_prefill_graph(self, items: Sequence[StepItem], starts: List[int], greedy: bool = False) -> Optional[torch.Tensor]:
         """One full portion of one prompt: the same work every time but for the index arrays, so it is
         recorded once (per number of wanted rows, 0 or 1, and per set of plans) and replayed over its own
         staging buffers."""
         T, R = len(items[0].tokens), len(items[0].want)
+        greedy = greedy and R == 1
         plans, plan_key, need = self._plan([T], starts, T, 1)
-        entry = self._graphs.get(("prefill", T, R, plan_key))
+        key = ("prefill", T, R, plan_key, greedy)
+        entry = self._graphs.get(key)
         if entry is None:
-            logits = self._record(("prefill", T, R, plan_key), items, starts, 1, R, plans, need)
+            logits = self._record(key, items, starts, 1, R, plans, need, greedy)
         else:
             self._build(items, starts, pad_to=1, buffers=entry["buffers"], scratch=entry["scratch"], rows=R,
-                        plans=entry["plans"])
+                        plans=entry["plans"], greedy=greedy)
             entry["graph"].replay()
             ops._count(entry["launches"])
             logits = entry["logits"]
         self.graph_replays += 1
         return logits
 
-    def _record(self, key, items: Sequence[StepItem], starts: List[int], S: int, R: int, plans, need: int) -> torch.Tensor:
+    def _record(self, key, items: Sequence[StepItem], starts: List[int], S: int, R: int, plans, need: int,
+                greedy: bool = False) -> Optional[torch.Tensor]:
         """First step of a shape: a graph keeps the addresses it was recorded with, so the shape owns its
         staging buffer and its scratch."""
         T = sum(len(it.tokens) for it in items) + (S - len(items))
         lay = _Layout(T, S, R, len(self.cache.groups), self.cache.max_blocks)
         buffers = _Staging(lay.total, self.device)
         scratch = torch.empty(need, dtype=torch.float32, device=self.device) if need > 0 else None
-        batch = self._build(items, starts, pad_to=S, buffers=buffers, scratch=scratch, rows=R, plans=plans)
+        batch = self._build(items, starts, pad_to=S, buffers=buffers, scratch=scratch, rows=R, plans=plans, greedy=greedy)
         return self._run_and_record(key, batch, {"buffers": buffers, "scratch": scratch, "plans": plans})
 
     def _run_and_record(self, key, batch: Batch, entry: dict) -> torch.Tensor:

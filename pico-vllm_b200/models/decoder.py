@@ -88,7 +88,8 @@ class DecoderModel:
 
     def forward(self, batch, views: Sequence[CacheView]) -> torch.Tensor:
         """Runs the batch's tokens through every call of the order; returns float32 logits
-        [len(batch.logit_rows), vocab]."""
+        [len(batch.logit_rows), vocab] - or None when ``batch.greedy_out`` was given and the head wrote the
+        greedy token of every wanted row there instead."""
         x = self.embed.forward(batch.token_ids, batch.feedback)
         if self.embed_position is not None:
             x = self.embed_position.add_to(x, batch.positions)
@@ -102,8 +103,13 @@ class DecoderModel:
             x, pending = self.blocks[call.block].forward(x, pending, batch, view)
         if batch.num_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=x.device)
+        greedy = getattr(batch, "greedy_out", None) if hasattr(self.head, "greedy") else None
         if pending is None and hasattr(self.head, "can_fuse_norm") \
                 and self.head.can_fuse_norm(x, self.final_norm, batch.num_logit_rows):
+            if greedy is not None and self.head.greedy(x, self.final_norm, batch.logit_rows, batch.num_logit_rows, greedy):
+                return None
             return self.head.forward_normed(x, self.final_norm, batch.logit_rows)
         y = self.final_norm.add_norm(x, pending, rows=batch.logit_rows)
+        if greedy is not None and self.head.greedy(y, None, None, batch.num_logit_rows, greedy):
+            return None
         return self.head.forward(y)

@@ -56,6 +56,7 @@ def library():
         "pico_paged_decode_mma": [vp, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32,
                                   f32, i32, vp],
         "pico_skinny_linear": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp, f32, vp, vp],
+        "pico_skinny_argmax": [vp, i32, vp, vp, i32, i32, i32, vp, f32, vp, vp],
         "pico_skinny_norm_fits": [i32, i32],
         "pico_skinny_linear_residual": [vp, i32, vp, vp, i32, i32, i32, vp],
         "pico_skinny_gate_up_swiglu": [vp, i32, vp, vp, i32, i32, i32, vp, f32, vp],
@@ -478,6 +479,29 @@ def skinny_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     _check(library().pico_skinny_linear(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), _ptr(out), N,
                                         1 if out_dtype == torch.float32 else 0, M, N, K, _ptr(norm_weight),
                                         float(eps), _ptr(rows), _stream()), "skinny_linear")
+    _count()
+    return out
+
+
+def skinny_argmax(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, norm_weight: Optional[torch.Tensor] = None,
+                  eps: float = 0.0, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[m] = the first n with the largest (x weight^T)[m, n]: the greedy choice of an output head in the
+    product's own epilogue, without writing the [M, N] logits.  x [M <= 16, K] bfloat16, or with ``norm_weight``
+    the float32 residual stream, RMS-normed on the way in (``rows`` int32 picks its rows); out int32, at least M
+    long.  Calls must follow one another on one stream (they share a table of partial results)."""
+    _cuda(x, weight, out, norm_weight, rows)
+    if _norm_args(x, norm_weight, "skinny_argmax") is not None:
+        M = rows.shape[0] if rows is not None else x.shape[0]
+        if not skinny_norm_takes(x, weight, M) or (rows is not None and rows.dtype != torch.int32):
+            raise KernelError("skinny_argmax: sizes not taken with a fused norm")
+    else:
+        if not skinny_takes(x, weight):
+            raise KernelError("skinny_argmax: needs bfloat16, at most 16 tokens, K and N multiples of 16")
+        M = x.shape[0]
+    if out.dtype != torch.int32 or out.dim() != 1 or out.shape[0] < M or not out.is_contiguous():
+        raise KernelError("skinny_argmax: out must be int32 with room for one token per row")
+    _check(library().pico_skinny_argmax(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), M, weight.shape[0], x.shape[1],
+                                        _ptr(norm_weight), float(eps), _ptr(rows), _stream()), "skinny_argmax")
     _count()
     return out
 

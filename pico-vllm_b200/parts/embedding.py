@@ -52,3 +52,19 @@ class OutputHead(Part):
     def forward_normed(self, x: torch.Tensor, norm, rows: torch.Tensor) -> torch.Tensor:
         """Logits of rows ``rows`` of the residual stream x, with the last norm applied inside the kernel."""
         return ops.skinny_linear(x, self.matrix(), None, torch.float32, norm.weight, norm.eps, rows)
+
+    def greedy(self, x: torch.Tensor, norm, rows: Optional[torch.Tensor], n_rows: int, out: torch.Tensor) -> bool:
+        """The greedy tokens of ``n_rows`` rows straight into ``out`` (int32), without logits: argmax in the
+        product's epilogue.  With ``norm``, x is the residual stream and the last norm runs inside the kernel
+        (``rows`` picks its rows); without, x is already normed.  False when the fused kernel does not take
+        the sizes: the caller then computes logits."""
+        w = self.matrix()
+        if norm is not None:
+            if not self.can_fuse_norm(x, norm, n_rows):
+                return False
+            ops.skinny_argmax(x, w, out, norm.weight, norm.eps, rows)
+            return True
+        if not ops.skinny_takes(x, w):
+            return False
+        ops.skinny_argmax(x, w, out)
+        return True

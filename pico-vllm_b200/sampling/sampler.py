@@ -76,6 +76,23 @@ class Sampler:
             event.record()
         return PendingTokens(host, event, R)
 
+    def tokens_from(self, tokens: torch.Tensor, n: int) -> PendingTokens:
+        """The first ``n`` tokens of an int32 device tensor that a kernel has been launched to fill, on their way
+        to the host without waiting (``result()`` waits)."""
+        cuda = self.device.type == "cuda"
+        if self._host[self._turn] is None or self._host[self._turn].numel() < max(n, 1):
+            self._host[self._turn] = torch.empty(max(64, n), dtype=torch.int32, pin_memory=cuda)
+        host = self._host[self._turn]
+        self._turn ^= 1
+        if n == 0:
+            return PendingTokens(host, None, 0)
+        host[:n].copy_(tokens[:n], non_blocking=True)
+        event = None
+        if cuda:
+            event = torch.cuda.Event()
+            event.record()
+        return PendingTokens(host, event, n)
+
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], top_ps: Sequence[float],
                uniforms: Optional[Sequence[float]] = None) -> List[int]:
         """logits float32 [R, V] on the device -> R token ids (host ints; one device-to-host read)."""

@@ -140,6 +140,12 @@ def skinny_linear(x, weight, bias=None, out_dtype=torch.bfloat16, norm_weight=No
     return y.to(out_dtype)
 
 
+def skinny_argmax(x, weight, out, norm_weight=None, eps=0.0, rows=None):
+    logits = skinny_linear(x, weight, None, torch.float32, norm_weight, eps, rows)
+    out[:logits.shape[0]] = logits.argmax(-1).to(out.dtype)
+    return out
+
+
 def skinny_linear_residual(x, weight, residual):
     residual.add_(x.float() @ weight.float().t())
 

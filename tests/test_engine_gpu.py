@@ -55,6 +55,53 @@ def test_every_cutting_matches_plain(dtype, name, cut, graph):
     assert all(g.pool.in_use == 0 for g in runner.cache.groups)
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_greedy_tokens_chosen_inside_the_head_are_the_argmax_of_its_logits(graph):
+    """``step(..., greedy=True)`` leaves the tokens in ``runner.feedback`` and writes no logits where the head's
+    kernel can choose them (bfloat16, up to 16 wanted rows, a vocabulary that is a multiple of 16): the same steps
+    through a second runner with logits must give the same tokens, for decode steps (recorded and replayed),
+    a mixed step, and a step where not every row is wanted."""
+    from pico_vllm_b200.engine import StepItem
+    name = "a"
+    cfg = helpers.tiny_config(name)
+    ra, _ = helpers.make_runner_from_tensors(name, "bfloat16", DEV, 512, max_num_seqs=8, use_cuda_graph=graph)
+    rb, _ = helpers.make_runner_from_tensors(name, "bfloat16", DEV, 512, max_num_seqs=8, use_cuda_graph=graph)
+    prompts = [helpers.random_ids(n, cfg.vocab_size, 700 + n) for n in (9, 30, 4, 17, 22)]
+    sa = [ra.cache.acquire(i) for i in range(5)]
+    sb = [rb.cache.acquire(i) for i in range(5)]
+    # a mixed step: three prompts whole, rows wanted at their ends
+    items = lambda slots, toks, want: [StepItem(s, t, w) for s, t, w in zip(slots, toks, want)]
+    want = [(len(p) - 1,) for p in prompts[:3]]
+    assert ra.step(items(sa[:3], prompts[:3], want), greedy=True) is None
+    logits = rb.step(items(sb[:3], prompts[:3], want))
+    last = logits.argmax(-1).tolist()
+    assert ra.feedback[:3].tolist() == last
+    for k in range(6):                              # decode steps: 3, then 5 requests (two join with their prompts first)
+        if k == 2:
+            w2 = [(len(p) - 1,) for p in prompts[3:]]
+            assert ra.step(items(sa[3:], prompts[3:], w2), greedy=True) is None
+            last += rb.step(items(sb[3:], prompts[3:], w2)).argmax(-1).tolist()
+            assert ra.feedback[:2].tolist() == last[3:]
+        n = len(last)
+        toks = [[t] for t in last]
+        out = ra.step(items(sa[:n], toks, [(0,)] * n), greedy=True)
+        assert out is None
+        last = rb.step(items(sb[:n], toks, [(0,)] * n)).argmax(-1).tolist()
+        assert ra.feedback[:n].tolist() == last, f"decode step {k}"
+    # not every row wanted: tokens of the wanted rows, in order (a recorded step computes every row of its
+    # bucket, so there logits come back instead, for the wanted rows only)
+    n = len(last)
+    out = ra.step(items(sa[:n], [[t] for t in last], [(0,), (), (0,), (), (0,)]), greedy=True)
+    ref = rb.step(items(sb[:n], [[t] for t in last], [(0,), (), (0,), (), (0,)]))
+    assert ref.shape == (3, cfg.vocab_size)
+    if graph:
+        assert out is not None and out.shape == ref.shape and torch.equal(out.argmax(-1), ref.argmax(-1))
+    else:
+        assert out is None and ra.feedback[:3].tolist() == ref.argmax(-1).tolist()
+    if graph:
+        assert ra.graph_replays >= 6
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cut", ["tail", "mixed"])
 def test_a_model_2048_wide(dtype, cut):

@@ -506,3 +506,49 @@ def test_sample_distribution():
     freq = torch.bincount(out.cpu().long(), minlength=V).double() / N
     probs = torch.softmax(logits[0].double() / 1.5, 0)
     assert float((freq - probs).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
+@pytest.mark.parametrize("N,K", [(336, 80), (4096, 1536), (151936, 1536)])
+@pytest.mark.parametrize("normed", [False, True])
+def test_skinny_argmax_is_the_first_largest_logit(M, N, K, normed):
+    """The greedy head: the token is chosen in the product's epilogue.  It must be the argmax of the logits the
+    same kernel family writes (the sums are the same), and the first of equal logits: rows 5 and N - 7 of the
+    weights are made equal and dominant for token 0."""
+    from pico_vllm_b200 import ops
+    T = M + 2
+    xf = torch.randn(T, K, generator=gen(140)) * 2
+    w = (torch.randn(N, K, generator=gen(141)) / math.sqrt(K)).to(torch.bfloat16)
+    nw = 1 + 0.1 * torch.randn(K, generator=gen(142))
+    rows = torch.randperm(T, generator=gen(143))[:M].to(torch.int32)
+    if normed:
+        if not ops.skinny_norm_takes(xf.to(DEV), w.to(DEV), M):
+            pytest.skip("the fused norm does not take this many rows of this width")
+        x_eff = fake_ops._normed(xf, nw, 1e-5)[rows.long()]
+    else:
+        x_eff = xf[:M].to(torch.bfloat16)
+    big = (x_eff[0].float() / x_eff[0].float().norm() * 3).to(torch.bfloat16)
+    w[5] = big
+    w[N - 7] = big
+    out = torch.full((M + 3,), -1, dtype=torch.int32, device=DEV)
+    if normed:
+        ops.skinny_argmax(xf.to(DEV), w.to(DEV), out, nw.to(DEV), 1e-5, rows.to(DEV))
+        logits = ops.skinny_linear(xf.to(DEV), w.to(DEV), None, torch.float32, nw.to(DEV), 1e-5, rows.to(DEV))
+    else:
+        ops.skinny_argmax(x_eff.to(DEV), w.to(DEV), out)
+        logits = ops.skinny_linear(x_eff.to(DEV), w.to(DEV), None, torch.float32)
+    got = out.cpu()
+    assert got[M:].tolist() == [-1, -1, -1]                         # nothing written past the rows
+    assert got[:M].tolist() == logits.cpu().argmax(-1).tolist()     # on the CPU torch's argmax returns the first of equals
+    assert got[0] == 5
+    # and against the plain product: the chosen logit is (nearly) the largest
+    ref = x_eff.float() @ w.float().t()
+    picked = ref[torch.arange(M), got[:M].long()]
+    assert float((ref.max(-1).values - picked).max()) <= 2e-2 * float(ref.abs().max())
+    # twice in a row: the second launch finds the first one's counters cleared
+    out2 = torch.full((M,), -1, dtype=torch.int32, device=DEV)
+    if normed:
+        ops.skinny_argmax(xf.to(DEV), w.to(DEV), out2, nw.to(DEV), 1e-5, rows.to(DEV))
+    else:
+        ops.skinny_argmax(x_eff.to(DEV), w.to(DEV), out2)
+    assert out2.cpu().tolist() == got[:M].tolist()
