@@ -14,7 +14,13 @@ step of the whole batch.  Prints ONE JSON line:
 * ``prefill``: one 2,048-token prompt through the step function;
 * ``roofline``: bytes a decode step has to read (every weight once, the cache of the live
   requests) / its time, against the measured copy bandwidth;
-* ``points``: decode tokens per second at batch 1 and 64.
+* ``points``: decode at batch 1 and 64 at the same context (tokens per second, ms per step, fraction of the
+  roofline), and the reference's own decode workload - a 512-token prompt, then 256 generated tokens, the 256
+  steps timed - at batch 1, 8 and 64 (``gen256_b*``).
+
+Every timed decode step also chooses its tokens (greedy; for up to 16 rows inside the head's kernel).
+``--config 3b`` and ``--config 7b`` run the two larger shapes of the architecture with the workloads named for
+them (``run_shape``); ``--impl reference`` runs the unmodified reference engine (``baseline/reference_arm.py``).
 
 The weights and the cache of every timed step are far larger than the 126 MB L2, so no L2 flush
 is needed between iterations (``config.l2`` says so).  Peaks come from MEASURED_PEAKS.json when
@@ -40,6 +46,14 @@ MODEL = dict(architectures=["Qwen2ForCausalLM"], vocab_size=151936, hidden_size=
              rms_norm_eps=1e-6, tie_word_embeddings=True, use_sliding_window=False,
              max_position_embeddings=32768, hidden_act="silu")
 FULL_LAYERS = 28
+# the two larger shapes of the same architecture (--config 3b / 7b): their own workloads, see run_shape
+SHAPES = {
+    "1.5b": ("Qwen2.5-1.5B shape", MODEL),
+    "3b": ("Qwen2.5-3B shape", dict(MODEL, hidden_size=2048, num_hidden_layers=36, num_attention_heads=16,
+                                    intermediate_size=11008)),
+    "7b": ("Qwen2.5-7B shape", dict(MODEL, vocab_size=152064, hidden_size=3584, num_attention_heads=28,
+                                    num_key_value_heads=4, intermediate_size=18944, tie_word_embeddings=False)),
+}
 
 
 def peaks():
@@ -178,8 +192,9 @@ def decode_phase(llm, batch, context, steps, warmup, seed):
             runner.step([StepItem(s, torch.randint(0, V, (n,), generator=g).tolist(), ())])
             at += n
     toks = torch.randint(0, V, (steps + warmup, batch), generator=g).tolist()
+    # every step chooses its tokens (greedy, inside the head's kernel where it can), as a serving step does
     for i in range(warmup):
-        runner.step([StepItem(s, [toks[i][j]], (0,)) for j, s in enumerate(slots)])
+        runner.step([StepItem(s, [toks[i][j]], (0,)) for j, s in enumerate(slots)], greedy=True)
     torch.cuda.synchronize()
     before = ops.launches
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -187,7 +202,9 @@ def decode_phase(llm, batch, context, steps, warmup, seed):
         torch.cuda.profiler.start()
     t0.record()
     for i in range(warmup, warmup + steps):
-        runner.step([StepItem(s, [toks[i][j]], (0,)) for j, s in enumerate(slots)])
+        logits = runner.step([StepItem(s, [toks[i][j]], (0,)) for j, s in enumerate(slots)], greedy=True)
+        if logits is not None:                       # more rows than the head's kernel chooses among: the sampling kernel
+            llm.sampler.sample_async(logits, [0.0] * batch, [1.0] * batch, None, out=runner.feedback)
     t1.record()
     torch.cuda.synchronize()
     if PROFILE_RANGE == "decode":
@@ -386,6 +403,139 @@ def run_micro(args):
     return 0
 
 
+def random_model_on_device(raw, device="cuda:0", seed=0):
+    """A model of the given configuration with random weights drawn on the device (the larger shapes: drawing
+    7.6 G normal numbers on the host and writing them to a folder would take minutes); bfloat16 matrices, float32
+    vectors, N(0, 0.02) and 1 + N(0, 0.02) for norm weights, as the random-weights mode writes them."""
+    import torch
+    from pico_vllm_b200.engine.core import _prepare_precision
+    from pico_vllm_b200.registry import build_model, config_from_dict
+    cfg = config_from_dict(raw)
+    model = build_model(cfg)
+    _prepare_precision("bfloat16")
+    g = torch.Generator(device=device).manual_seed(seed)
+    for b in model.bindings:
+        for p in b.part.params():
+            t = torch.randn(p.shape, generator=g, device=device, dtype=torch.float32) * 0.02
+            if p.init == "one_plus_normal":
+                t = t + 1.0
+            b.part.assign(p.attr, t if p.kind == "vector" else t.to(torch.bfloat16))
+    model.materialize(device, torch.bfloat16)
+    return cfg, model
+
+
+def step_flops(cfg, q_lens, starts):
+    """Floating-point operations of one step: the products of every token, attention over each token's visible
+    keys, and the head for one row per segment."""
+    H, I, V, L = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size, cfg.num_hidden_layers
+    nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    per_tok = 2 * (H * (nh + 2 * nkv) * hd + nh * hd * H + 2 * H * I + I * H)
+    attn = sum(4 * nh * hd * (n * st + n * (n + 1) / 2) for n, st in zip(q_lens, starts))
+    return L * (per_tok * sum(q_lens) + attn) + 2 * H * V * len(q_lens)
+
+
+def run_shape(args):
+    """The two larger shapes of the architecture with the workloads named for them: 3b - continuous batching of
+    32 requests (prompts of 64 to 2,048 tokens, 128 generated tokens each) through ``LLM.generate``; 7b - decode
+    steps of 64 requests at context 8,192, and steps that hold one 2,048-token portion of a prompt beside 63
+    decoding requests.  Prints one JSON line."""
+    import torch
+    import pico_vllm_b200  # noqa: F401
+    from pico_vllm_b200 import LLM, SamplingParams, ops
+    from pico_vllm_b200.engine import StepItem
+    pk = peaks()
+    name, raw = SHAPES[args.config]
+    raw = dict(raw, num_hidden_layers=args.layers or raw["num_hidden_layers"])
+    t0 = time.time()
+    cfg, model = random_model_on_device(raw)
+    print(f"[bench] {name}: random weights on the device in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    out = {"impl": "ours", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
+           "config": {"model": name, "layers": cfg.num_hidden_layers, "layers_full": SHAPES[args.config][1]["num_hidden_layers"],
+                      "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                      "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                      "tied": cfg.tie_word_embeddings, "page_size": 16, "peaks": pk["source"]}}
+    sampler = ClockSampler()
+    if args.config == "3b":
+        n_req, n_new = 32, 128
+        llm = LLM(model, dtype="bfloat16", page_size=16, num_pages=n_req * ((2048 + n_new) // 16 + 2), max_num_seqs=n_req,
+                  max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=2048 + n_new + 16)
+        wbytes = weight_bytes(llm.model)
+        sp = SamplingParams(temperature=0.0, max_new_tokens=n_new, ignore_eos=True)
+
+        def workload(seed):
+            g = torch.Generator().manual_seed(seed)
+            lens = torch.randint(64, 2049, (n_req,), generator=g).tolist()
+            return [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+        llm.generate(workload(1), sp)                        # the same workload once before: graphs recorded, libraries warm
+        prompts = workload(2)
+        steps0 = llm.stats["steps"]
+        torch.cuda.synchronize()
+        sampler.start()
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, sp)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        clocks = sampler.stop()
+        steps = llm.stats["steps"] - steps0
+        n_prompt = sum(len(p) for p in prompts)
+        assert all(len(o.token_ids) == n_new for o in outs)
+        out.update({"metric": f"generated tok/s end to end ({name}, {n_req} requests, prompts 64..2048, {n_new} new tokens each)",
+                    "value": round(n_req * n_new / dt, 1), "unit": "tok/s", "seconds": round(dt, 4), "steps": steps,
+                    "prompt_tokens": n_prompt, "all_tokens_per_s": round((n_prompt + n_req * n_new) / dt, 1),
+                    "ms_per_step": round(dt * 1000.0 / steps, 4), "preemptions": llm.scheduler.num_preemptions,
+                    # every step reads every weight at least once: a lower bound of the bytes moved
+                    "roofline": {"bound": "hbm", "achieved": round(steps * wbytes / dt / 1e9, 1), "peak": pk["hbm_gbs"],
+                                 "unit": "GB/s", "frac": round(steps * wbytes / dt / 1e9 / pk["hbm_gbs"], 4),
+                                 "note": "weights only, once per step"},
+                    "clocks": clocks})
+    else:
+        batch, context = 64, 8192
+        llm = LLM(model, dtype="bfloat16", page_size=16, num_pages=batch * ((context + 2048 + 128) // 16 + 1) + 64,
+                  max_num_seqs=batch, max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=context + 6 * 2048)
+        wbytes = weight_bytes(llm.model)
+        kvb = kv_bytes_per_token(llm.model, llm.cache)
+        sampler.start()
+        ms, launches = decode_phase(llm, batch, context, args.steps, args.warmup, seed=1)
+        clocks = sampler.stop()
+        step_bytes = wbytes + batch * (context - args.steps / 2) * kvb
+        # one 2,048-token portion of a prompt beside 63 decoding requests at context 8,192
+        runner, cache = llm.runner, llm.cache
+        g = torch.Generator().manual_seed(5)
+        V = cfg.vocab_size
+        slots = [cache.acquire(f"d{i}") for i in range(63)]
+        for s_ in slots:
+            for at in range(0, context - 64, 2048):
+                n = min(2048, context - 64 - at)
+                runner.step([StepItem(s_, torch.randint(0, V, (n,), generator=g).tolist(), ())])
+        big = cache.acquire("p")
+        times, fl = [], 0.0
+        for rep in range(5):
+            items = [StepItem(big, torch.randint(0, V, (2048,), generator=g).tolist(), (2047,))]
+            items += [StepItem(s_, [int(torch.randint(0, V, (1,), generator=g))], (0,)) for s_ in slots]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            runner.step(items)
+            b.record()
+            torch.cuda.synchronize()
+            if rep >= 2:
+                times.append(a.elapsed_time(b))
+                fl = step_flops(cfg, [2048] + [1] * 63, [rep * 2048] + [context - 64 + rep] * 63)
+        times.sort()
+        mixed_ms = times[len(times) // 2]
+        out.update({"metric": f"decode tok/s ({name}, batch {batch}, context {context})",
+                    "value": round(batch / ms * 1000.0, 1), "unit": "tok/s", "steps": args.steps, "warmup": args.warmup,
+                    "ms_per_step": round(ms, 4), "launches_per_step": round(launches, 1),
+                    "roofline": {"bound": "hbm", "achieved": round(step_bytes / (ms / 1e3) / 1e9, 1), "peak": pk["hbm_gbs"],
+                                 "unit": "GB/s", "frac": round(step_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)},
+                    "mixed": {"what": "one 2,048-token portion beside 63 decoding requests at context 8,192",
+                              "ms_per_step": round(mixed_ms, 3), "tokens_per_s": round((2048 + 63) / mixed_ms * 1e3, 1),
+                              "frac": round(fl / (mixed_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "bound": "bf16 tensor"},
+                    "clocks": clocks})
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
     import torch
     if not torch.cuda.is_available():
@@ -427,11 +577,22 @@ def run_ours(args):
 
     e2e_ms = e2e_phase(llm, batch, context, args.steps, args.warmup, seed=2)
     pre_ms = prefill_phase(llm, T, reps=5, seed=3)
+    def frac(b, ctx_mid, step_ms):
+        return round((wbytes + b * ctx_mid * kvb) / (step_ms / 1000.0) / 1e9 / pk["hbm_gbs"], 4)
+
     points = {}
     if not args.no_points:
         for b in (1, 64):
             pms, _ = decode_phase(llm, b, context, 32, 8, seed=10 + b)
             points[f"decode_b{b}"] = round(b / pms * 1000.0, 1)
+            points[f"decode_b{b}_ms"] = round(pms, 4)
+            points[f"decode_b{b}_frac"] = frac(b, context - 16, pms)
+        # the reference's own decode workload: a 512-token prompt, then 256 generated tokens (the 256 steps are timed)
+        for b in (1, 8, 64):
+            pms, _ = decode_phase(llm, b, 512 + 8 + 256, 256, 8, seed=20 + b)
+            points[f"gen256_b{b}"] = round(b / pms * 1000.0, 1)
+            points[f"gen256_b{b}_ms"] = round(pms, 4)
+            points[f"gen256_b{b}_frac"] = frac(b, 512 + 8 + 128, pms)
 
     step_bytes = wbytes + batch * (context - args.steps / 2) * kvb
     achieved = step_bytes / (ms / 1000.0) / 1e9
@@ -441,7 +602,7 @@ def run_ours(args):
     bucket = llm.runner._bucket(batch)
     stage = max(e["buffers"].host.numel() for k, e in llm.runner._graphs.items() if k[:2] == ("decode", bucket)) * 4
     out = {
-        "metric": "decode tok/s (Qwen2.5-1.5B shape, batch 8, context 4096)",
+        "metric": f"decode tok/s (Qwen2.5-1.5B shape, batch {batch}, context {context})",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights N(0, 0.02)",
@@ -450,7 +611,7 @@ def run_ours(args):
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "tied": cfg.tie_word_embeddings, "global_batch": batch, "seq_len": context,
-                   "page_size": 16, "parallelism": "single GPU", "cuda_graph": True,
+                   "page_size": 16, "parallelism": "single GPU", "cuda_graph": True, "sampling": "greedy, in the head's kernel",
                    "l2": "no flush: each step reads >3 GB of weights and cache, L2 is 126 MB",
                    "peaks": pk["source"]},
         "clocks": clocks,
@@ -478,7 +639,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (named in config)")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (named in config)")
+    ap.add_argument("--config", choices=sorted(SHAPES), default="1.5b",
+                    help="1.5b: the default run; 3b, 7b: the larger shapes with the workloads named for them")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one phase only and print a short line (for profiling; not a bench value)")
@@ -491,6 +654,12 @@ def main():
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (this engine runs on a single GPU)")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.config == "1.5b":
+        args.layers = args.layers or FULL_LAYERS
+    if args.impl == "reference" and args.config != "1.5b":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference has the Qwen2.5-1.5B shape only "
+                                                              "(pico_vllm/model.py:15-26)"}))
+        return 0
     if args.impl == "reference":
         # the unmodified reference from baseline/_ref through its own Engine.submit / Engine.step; nothing of this
         # repository's package is imported on that path
@@ -511,6 +680,8 @@ def main():
         args.no_points = True
     if args.micro:
         return run_micro(args)
+    if args.config != "1.5b":
+        return run_shape(args)
     return run_ours(args)
 
 

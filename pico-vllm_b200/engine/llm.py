@@ -42,7 +42,8 @@ class RequestOutput:
 class LLM:
     def __init__(self, model: str, dtype: str = "bfloat16", engine_config: Optional[EngineConfig] = None,
                  tokenizer=None, **engine_options):
-        """``model``: folder with config.json and safetensors.  ``engine_options`` are fields of
+        """``model``: folder with config.json and safetensors (or a model object that already has its
+        weights on the device, as ``engine.load_model`` returns).  ``engine_options`` are fields of
         EngineConfig (page_size, num_pages, max_cache_tokens, max_num_seqs,
         max_num_batched_tokens, prefill_chunk, max_model_len, use_cuda_graph, seed, device)."""
         if engine_config is None:
@@ -50,11 +51,12 @@ class LLM:
         elif engine_options:
             raise ConfigError("give either engine_config or separate engine options, not both")
         self.cfg = engine_config
-        self.model = load_model(model, self.cfg)
+        self.model = load_model(model, self.cfg) if isinstance(model, (str, os.PathLike)) else model
         self.cache = make_cache(self.model, self.cfg)
         self.runner = ModelRunner(self.model, self.cache, self.cfg)
         self.sampler = Sampler(self.cfg.device, self.cfg.seed)
-        self.tokenizer = tokenizer if tokenizer is not None else _maybe_tokenizer(model)
+        self.tokenizer = tokenizer if tokenizer is not None else (
+            _maybe_tokenizer(model) if isinstance(model, (str, os.PathLike)) else None)
         eos = getattr(self.model.config, "eos_token_id", None)
         if eos is None and self.tokenizer is not None:
             eos = getattr(self.tokenizer, "eos_token_id", None)
