@@ -489,9 +489,9 @@ def run_shape(args):
                                  "note": "weights only, once per step"},
                     "clocks": clocks})
     else:
-        batch, context = 64, 8192
-        llm = LLM(model, dtype="bfloat16", page_size=16, num_pages=batch * ((context + 2048 + 128) // 16 + 1) + 64,
-                  max_num_seqs=batch, max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=context + 6 * 2048)
+        batch, context = args.batch or 64, args.context or 8192
+        llm = LLM(model, dtype="bfloat16", page_size=16, num_pages=max(batch, 64) * ((context + 2048 + 128) // 16 + 1) + 64,
+                  max_num_seqs=max(batch, 64), max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=context + 6 * 2048)
         wbytes = weight_bytes(llm.model)
         kvb = kv_bytes_per_token(llm.model, llm.cache)
         sampler.start()
@@ -637,8 +637,8 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=None, help="decoding requests (default 8; 64 for --config 7b)")
+    ap.add_argument("--context", type=int, default=None, help="context length of the decode steps (default 4096; 8192 for --config 7b)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (named in config)")
     ap.add_argument("--config", choices=sorted(SHAPES), default="1.5b",
                     help="1.5b: the default run; 3b, 7b: the larger shapes with the workloads named for them")
@@ -654,8 +654,10 @@ def main():
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported (this engine runs on a single GPU)")
         return 2
     args.warmup = max(args.warmup, 3)
-    if args.config == "1.5b":
+    if args.config == "1.5b" or args.micro:
         args.layers = args.layers or FULL_LAYERS
+        args.batch = args.batch or 8
+        args.context = args.context or 4096
     if args.impl == "reference" and args.config != "1.5b":
         print(json.dumps({"impl": "reference", "unavailable": "the reference has the Qwen2.5-1.5B shape only "
                                                               "(pico_vllm/model.py:15-26)"}))
