@@ -28,7 +28,6 @@ import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref", "pico_vllm")
-REF_SOURCE = "/root/reference/pico_vllm"
 
 SHAPE = dict(vocab_size=151936, hidden_size=1536, num_hidden_layers=28, num_attention_heads=12,
              num_key_value_heads=2, intermediate_size=8960)
@@ -49,13 +48,17 @@ class StandInTokenizer:
 
 
 def ensure_reference():
+    """``baseline/_ref/pico_vllm`` must hold an unmodified copy of the reference's ``pico_vllm`` folder; when it
+    does not and PICO_REFERENCE_SOURCE names a checkout of the reference, the folder is copied from there."""
     if os.path.isfile(os.path.join(REF_DIR, "engine.py")):
         return
-    if os.path.isdir(REF_SOURCE):
+    source = os.environ.get("PICO_REFERENCE_SOURCE")
+    if source and os.path.isdir(os.path.join(source, "pico_vllm")):
         os.makedirs(os.path.dirname(REF_DIR), exist_ok=True)
-        shutil.copytree(REF_SOURCE, REF_DIR)
+        shutil.copytree(os.path.join(source, "pico_vllm"), REF_DIR)
         return
-    raise FileNotFoundError(f"{REF_DIR} is missing and {REF_SOURCE} is not mounted")
+    raise FileNotFoundError("baseline/_ref/pico_vllm is missing: copy the reference's pico_vllm folder there "
+                            "(or set PICO_REFERENCE_SOURCE to a checkout of the reference)")
 
 
 def write_random_weights(folder, layers, seed=0):
