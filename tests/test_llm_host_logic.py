@@ -113,3 +113,19 @@ def test_pages_held_by_a_request_in_flight_are_waited_for(monkeypatch, tmp_path,
         assert o.token_ids == plain.greedy_generate(p, tensors, helpers.plain_config(cfg), ps)
     llm.cache.check()
     assert all(g.pool.in_use == 0 for g in llm.cache.groups)
+
+
+def test_a_bounded_wait_that_ran_out_is_an_error_not_tokens(monkeypatch, tmp_path):
+    """The kernels' waits are bounded; a wait that runs out leaves a status word set and part of a result
+    unwritten.  The entry point reads the words before tokens leave it (when a request completes)."""
+    from pico_vllm_b200 import SamplingParams, ops
+    from pico_vllm_b200.errors import KernelError
+    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=256)
+    monkeypatch.setattr(ops, "_lib", object())          # as if the library were loaded
+    for name in ("tma_status", "tca_status", "tc_status"):
+        monkeypatch.setattr(ops, name, lambda: 0)
+    outs = llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_new_tokens=2, ignore_eos=True))
+    assert len(outs[0].token_ids) == 2
+    monkeypatch.setattr(ops, "tca_status", lambda: 1)
+    with pytest.raises(KernelError, match="paged_prefill_tcgen05"):
+        llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_new_tokens=2, ignore_eos=True))
