@@ -145,6 +145,27 @@ def test_decode_steps_of_many_live_requests(dtype, name, live, graph):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["b", "d", "e"])
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_cuttings_match_plain(dtype, name, seed):
+    """Random requests, cut at random: portions of 2 to 40 tokens or single tokens, up to four live, requests left
+    out of steps at random, graph replay on, a pool of exactly the live peak (pages come back and are used again)."""
+    import random
+    rng = random.Random(seed)
+    cfg = helpers.tiny_config(name)
+    reqs = {f"r{i}": helpers.random_ids(rng.randint(2, 180), cfg.vocab_size, 5000 + 10 * seed + i) for i in range(7)}
+    sizes = tuple(rng.choice([2, 3, 5, 8, 13, 21, 40]) for _ in range(9))
+    steps = helpers.trace_mixed(reqs, max_live=rng.randint(2, 4), seed=seed, chunk_sizes=sizes)
+    runner, tensors = helpers.make_runner_from_tensors(name, dtype, DEV, helpers.live_token_peak(steps), use_cuda_graph=True)
+    want = helpers.expected_logits(steps, reqs, _plain_logits(name, reqs, tensors))
+    for i, (g, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+        if w is not None:
+            assert torch.isfinite(g).all(), f"step {i}: not finite (a freed page was read?)"
+            helpers.assert_close_logits(g, w, REL[dtype], f"{name}/{dtype}/seed {seed} step {i}")
+    assert all(g.pool.in_use == 0 for g in runner.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["a", "b", "d"])
 def test_long_decoding(dtype, name):
     """A short prompt, then 400 tokens one by one (pages fill up, the window moves on)."""
