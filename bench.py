@@ -550,9 +550,10 @@ def run_ours(args):
     try:
         cfg = make_model_folder(layers, tmp)
         max_b = max(64, batch) if not args.no_points else batch
-        pages = max_b * ((context + 128) // 16 + 1) + 256
+        longest = max(context, 512 + 8 + 256, 2048) + 128     # the decode runs, the 512 + 256 workload, the 2,048-token prompt
+        pages = max_b * ((max(context, 512 + 8 + 256) + 128) // 16 + 1) + 256
         llm = LLM(tmp, dtype="bfloat16", page_size=16, num_pages=pages, max_num_seqs=max_b,
-                  max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=context + 128,
+                  max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=longest,
                   use_cuda_graph=True)
     finally:
         for f in os.listdir(tmp):

@@ -175,7 +175,7 @@ class LLM:
     def _launch(self, plan):
         items = []
         for s in plan:
-            toks = s.request.all_ids[s.start:s.start + s.count]
+            toks = s.request.tokens(s.start, s.count)
             items.append(StepItem(s.request.slot, toks, (s.count - 1,) if s.samples else ()))
             self.stats["decode_tokens" if s.request.is_decoding else "prefill_tokens"] += s.count
         rows = [s for s in plan if s.samples]
@@ -184,8 +184,11 @@ class LLM:
         return logits, rows
 
     def _sampling_args(self, rows):
+        temps = [r.request.temperature for r in rows]
+        if all(t <= 0 for t in temps):
+            return temps, None, None                # greedy rows need neither top-p nor random numbers
         seeds = [(r.request.seed if r.request.seed is not None else self.cfg.seed) for r in rows]
-        return ([r.request.temperature for r in rows], [r.request.top_p for r in rows],
+        return (temps, [r.request.top_p for r in rows],
                 [uniform_for(sd, r.request.request_id, len(r.request.generated_ids)) for sd, r in zip(seeds, rows)])
 
     def _encode(self, prompt: Prompt) -> List[int]:

@@ -60,6 +60,15 @@ class Request:
     def total_len(self) -> int:
         return len(self.prompt_ids) + len(self.generated_ids)
 
+    def tokens(self, start: int, count: int) -> List[int]:
+        """Tokens start .. start+count-1 of prompt + generated, without joining the two lists."""
+        n = len(self.prompt_ids)
+        if start >= n:
+            return self.generated_ids[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt_ids[start:start + count]
+        return self.prompt_ids[start:] + self.generated_ids[:start + count - n]
+
     @property
     def remaining(self) -> int:
         """Tokens that still have to go through the model before the next one can be sampled."""
@@ -142,6 +151,7 @@ class Scheduler:
                 reserve[i] += p
             plan.append(Scheduled(req, req.num_computed, n, req.num_computed + n == req.total_len))
             budget -= n
+
 
         # 1. running requests: one token for each decoding request first, then portions of
         #    prompts, oldest request first in both passes
