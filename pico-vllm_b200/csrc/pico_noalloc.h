@@ -38,7 +38,8 @@ extern "C" {
 //
 // It calls no cudaMalloc, cudaFree or any allocating routine.  The first call on a device looks
 // up the device address of the scratch array (cudaGetSymbolAddress, once per device, with that
-// device current); make that first call before any stream capture begins.  All calls share the
+// device current); make that first call before any stream capture begins.  Two host threads that make
+// their first calls on a device at the same moment both look the address up and both store the same value.  All calls share the
 // one array, which keeps what the last call left: nothing in it has to start at zero, because
 // every call writes each partial result before its second kernel reads it, but two calls whose
 // kernels overlap on the GPU (different streams, or different threads) race on it - keep calls
