@@ -196,7 +196,11 @@ class LLM:
             if self.tokenizer is None:
                 raise ConfigError("a text prompt needs a tokenizer; this model folder has none - pass token ids")
             return list(self.tokenizer.encode(prompt))
-        return [int(t) for t in prompt]
+        ids = [int(t) for t in prompt]
+        # negative ids have a meaning of their own inside the engine (a token still on the device): never a user's
+        if ids and not 0 <= min(ids) <= max(ids) < self.model.vocab_size:
+            raise ConfigError(f"prompt token ids must lie in [0, {self.model.vocab_size})")
+        return ids
 
     def _decode(self, ids: Sequence[int]) -> str:
         return self.tokenizer.decode(list(ids))

@@ -129,3 +129,14 @@ def test_a_bounded_wait_that_ran_out_is_an_error_not_tokens(monkeypatch, tmp_pat
     monkeypatch.setattr(ops, "tca_status", lambda: 1)
     with pytest.raises(KernelError, match="paged_prefill_tcgen05"):
         llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_new_tokens=2, ignore_eos=True))
+
+
+def test_prompt_token_ids_outside_the_vocabulary_are_refused(monkeypatch, tmp_path):
+    from pico_vllm_b200 import SamplingParams
+    from pico_vllm_b200.errors import ConfigError
+    llm = _llm(monkeypatch, tmp_path, "a", max_cache_tokens=256)
+    vocab = helpers.tiny_config("a").vocab_size
+    for bad in ([1, -3], [1, vocab]):
+        with pytest.raises(ConfigError, match="prompt token ids"):
+            llm.generate([bad], SamplingParams(max_new_tokens=2))
+    assert not llm.scheduler.has_work()
