@@ -93,7 +93,7 @@ class GQAAttention(Part):
     def can_fuse_norm(self, x: torch.Tensor, norm) -> bool:
         """True when forward can take the residual stream itself and apply ``norm`` inside its
         first kernel (small batches)."""
-        return hasattr(norm, "eps") and getattr(norm, "weight", None) is not None \
+        return getattr(norm, "plain_rms", False) and getattr(norm, "weight", None) is not None \
             and ops.skinny_norm_takes(x, self.qkv_weight)
 
     def forward(self, h: Optional[torch.Tensor], batch, cache: CacheView, residual: Optional[torch.Tensor] = None,

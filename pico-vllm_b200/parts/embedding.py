@@ -46,7 +46,7 @@ class OutputHead(Part):
         return ops.logits_linear(y, self.matrix())
 
     def can_fuse_norm(self, x: torch.Tensor, norm, n_rows: int) -> bool:
-        return hasattr(norm, "eps") and getattr(norm, "weight", None) is not None \
+        return getattr(norm, "plain_rms", False) and getattr(norm, "weight", None) is not None \
             and ops.skinny_norm_takes(x, self.matrix(), n_rows)
 
     def forward_normed(self, x: torch.Tensor, norm, rows: torch.Tensor) -> torch.Tensor:

@@ -31,7 +31,7 @@ class GatedMLP(Part):
                 Param("down_weight", (Piece("down.weight", (self.width, self.inner)),))]
 
     def can_fuse_norm(self, x: torch.Tensor, norm) -> bool:
-        return hasattr(norm, "eps") and getattr(norm, "weight", None) is not None and self.inner % 8 == 0 \
+        return getattr(norm, "plain_rms", False) and getattr(norm, "weight", None) is not None and self.inner % 8 == 0 \
             and ops.skinny_norm_takes(x, self.gate_up_weight)
 
     def forward(self, h: Optional[torch.Tensor], batch, residual: Optional[torch.Tensor] = None, norm=None):

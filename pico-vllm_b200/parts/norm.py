@@ -17,6 +17,10 @@ from .registry import register
 
 @register("norm", "rmsnorm")
 class RMSNorm(Part):
+    # y = x * rsqrt(mean(x^2) + eps) * weight and nothing else: what the product kernels with the norm inside
+    # compute.  A part that takes a norm into its own kernel asks for this mark, not for attribute names.
+    plain_rms = True
+
     def __init__(self, width: int, eps: float):
         self.width, self.eps = width, eps
         self.weight: Optional[torch.Tensor] = None

@@ -7,7 +7,10 @@ another mixer, cache need, position encoding and launch plan have to carry.
 * a mixer that keeps ONE latent vector per token in pages (a cache need of its own:
   ``PagedTensors``; no keys/values pair) and asks for scratch through ``plan``;
 * a learned absolute position encoding added at the embedding stage;
-* a rotary encoding that names a pairing the kernels do not have: refused, not computed wrongly.
+* a rotary encoding that names a pairing the kernels do not have: refused, not computed wrongly;
+* a norm of another kind (mean and variance, with a bias) and another arrangement of a layer
+  (the norm AFTER each residual add), both defined here, around the package's attention and
+  feed-forward.
 
 None of these is a model of the reference or of anyone's; the reference has one mixer, one cache
 shape and one position encoding (pico_vllm/model.py:126-227, pico_vllm/blockmanager.py:39-42).
@@ -21,7 +24,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _assemble(blocks, order, V, W, embed_position=None, seed=3):
+def _assemble(blocks, order, V, W, embed_position=None, seed=3, final_norm=None, dtype=torch.float32, scale=0.3):
     """A DecoderModel of the given blocks with random float32 tensors; returns (model, tensors)."""
     from pico_vllm_b200.parts import RMSNorm, TokenEmbedding, OutputHead
     from pico_vllm_b200.models import DecoderModel, Binding
@@ -33,8 +36,8 @@ def _assemble(blocks, order, V, W, embed_position=None, seed=3):
     for i, b in enumerate(blocks):
         for pn, part in b.parts().items():
             bindings.append(Binding(part, {pc.key: f"l{i}.{pn}.{pc.key}" for p in part.params() for pc in p.pieces}))
-    fn = RMSNorm(W, 1e-5)
-    bindings.append(Binding(fn, {"weight": "fn"}))
+    fn = final_norm if final_norm is not None else RMSNorm(W, 1e-5)
+    bindings.append(Binding(fn, {pc.key: ("fn" if pc.key == "weight" else f"fn.{pc.key}") for p in fn.params() for pc in p.pieces}))
     head = OutputHead(V, W, tied_to=embed)
 
     class Cfg:
@@ -46,10 +49,12 @@ def _assemble(blocks, order, V, W, embed_position=None, seed=3):
     for b in bindings:
         for p in b.part.params():
             for pc in p.pieces:
-                t = torch.randn(pc.shape, generator=g) * 0.3
+                t = torch.randn(pc.shape, generator=g) * scale
                 tensors[b.names[pc.key]] = t + 1 if p.init == "one_plus_normal" else t
-    load_state_dict(model, tensors, torch.float32, DEV)
-    model.materialize(DEV, torch.float32)
+    if dtype != torch.float32:      # what a folder stored in 16 bits holds: the matrices rounded, the vectors as they are
+        tensors = {k: (v.to(dtype).float() if v.dim() > 1 else v) for k, v in tensors.items()}
+    load_state_dict(model, {k: (v.to(dtype) if v.dim() > 1 else v) for k, v in tensors.items()}, dtype, DEV)
+    model.materialize(DEV, dtype)
     return model, tensors
 
 
@@ -284,3 +289,113 @@ def test_a_rotary_pairing_the_kernels_lack_is_refused():
     inv = torch.zeros(8, dtype=torch.float32, device=DEV)
     with pytest.raises(KernelError, match="pairing"):
         ops.skinny_qkv_rope_store(x, w, None, pos, inv, None, None, None, 2, 1, 16, 4, pairing="interleaved")
+
+
+# ------------------------------------------------------------------ another norm, another arrangement
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_norm_with_bias_in_a_post_norm_arrangement(dtype):
+    """The norm kind and the arrangement of a layer are parts like the others: a norm with mean, variance and
+    bias (``add_norm(x, delta, rows)`` is all a norm has to offer) and a block that norms AFTER each add
+    (``parts()`` and ``forward(x, pending, batch, cache) -> (x, pending)`` are all a block has to offer), around
+    the package's own attention and feed-forward, stepped whole, in mixed portions and from recorded graphs."""
+    from pico_vllm_b200.parts import Part, Param, Piece, register, make, GatedMLP, GQAAttention, Rotary
+    from pico_vllm_b200.models import LayerCall
+    import plain_qwen2 as plain
+    import torch.nn.functional as F
+
+    @register("norm", "toy_layer_norm")
+    class LayerNormWithBias(Part):
+        def __init__(self, width, eps):
+            self.width, self.eps = width, eps
+            self.weight = self.bias = None
+            self.act_dtype = torch.float32
+
+        def params(self):
+            return [Param("weight", (Piece("weight", (self.width,)),), kind="vector", init="one_plus_normal"),
+                    Param("bias", (Piece("bias", (self.width,)),), kind="vector")]
+
+        def materialize(self, device, dtype):
+            self.act_dtype = dtype
+
+        def stream(self, x, delta):
+            """norm(x + delta) as the new float32 residual stream (what a post-norm arrangement asks of its norm)."""
+            return F.layer_norm(x + delta.float(), (self.width,), self.weight.float(), self.bias.float(), self.eps)
+
+        def add_norm(self, x, delta, rows=None):
+            """What every norm offers: activations for the next part (here only the head asks)."""
+            if rows is not None:
+                r = rows.long()
+                x = x[r] + (delta[r].float() if delta is not None else 0)
+            elif delta is not None:
+                x += delta.float()
+            return F.layer_norm(x, (self.width,), self.weight.float(), self.bias.float(), self.eps).to(self.act_dtype)
+
+    class PostNormBlock:
+        def __init__(self, mixer, norm1, feed_forward, norm2):
+            self.mixer, self.norm1, self.feed_forward, self.norm2 = mixer, norm1, feed_forward, norm2
+
+        def parts(self):
+            return {"mixer": self.mixer, "norm1": self.norm1, "feed_forward": self.feed_forward, "norm2": self.norm2}
+
+        def forward(self, x, pending, batch, cache):
+            assert pending is None
+            x = self.norm1.stream(x, self.mixer.forward(x.to(self.norm1.act_dtype), batch, cache))
+            x = self.norm2.stream(x, self.feed_forward.forward(x.to(self.norm2.act_dtype), batch))
+            return x, None
+
+    W, V, hd, I = 48, 64, 16, 40         # sizes the small-batch kernels take: a norm they cannot compute must not reach them
+    tdtype, tolerance = (torch.float32, 5e-5) if dtype == "float32" else (torch.bfloat16, 3e-2)
+    def norm(eps):
+        return make("norm", "toy_layer_norm", width=W, eps=eps)
+    blocks = [PostNormBlock(GQAAttention(W, 2, 1, hd, position=Rotary(hd, 700.0)), norm(1e-5), GatedMLP(W, I), norm(1e-4)),
+              PostNormBlock(GQAAttention(W, 4, 2, hd, position=Rotary(hd, 9000.0), window=11), norm(1e-6), GatedMLP(W, I),
+                            norm(1e-5))]
+    # matrices of scale 0.12: the parts' outputs stay of the size of the normed stream they are added to (at 0.3 a
+    # feed-forward output is 25 against a stream of 3, and its rounding to bfloat16 alone is 1 % of the stream)
+    model, tensors = _assemble(blocks, [LayerCall(0, 0), LayerCall(1, 1)], V, W, seed=21, final_norm=norm(1e-5),
+                               dtype=tdtype, scale=0.12)
+
+    if dtype == "bfloat16":
+        # the head would take an RMS norm of these sizes into its own kernel; the toy norm it leaves alone
+        from pico_vllm_b200.parts import RMSNorm
+        rms = RMSNorm(W, 1e-5)
+        rms.weight = torch.ones(W, device=DEV)
+        stream = torch.zeros(4, W, device=DEV)
+        assert model.head.can_fuse_norm(stream, rms, 4) and not model.head.can_fuse_norm(stream, model.final_norm, 4)
+
+    def ln(x, name, eps):
+        return F.layer_norm(x, (W,), tensors[f"{name}.weight" if name != "fn" else "fn"], tensors[f"{name}.bias"], eps)
+
+    def attention(h, l, nh, nkv, theta, window):
+        T = h.shape[0]
+        w = {k[len(f"l{l}.mixer."):]: v for k, v in tensors.items() if k.startswith(f"l{l}.mixer.")}
+        q = (h @ w["q.weight"].T + w["q.bias"]).view(T, nh, hd)
+        k = (h @ w["k.weight"].T + w["k.bias"]).view(T, nkv, hd)
+        v = (h @ w["v.weight"].T + w["v.bias"]).view(T, nkv, hd)
+        pos = torch.arange(T)
+        cos, sin = plain.rotary_angles(pos.float(), hd, theta)
+        o = plain.attention_scores_softmax_pv(plain.apply_rotary(q, cos, sin), plain.apply_rotary(k, cos, sin), v, pos, window)
+        return o.reshape(T, nh * hd) @ w["o.weight"].T
+
+    def reference(ids):
+        x = plain.embed(torch.tensor(ids), tensors["emb"])
+        for l, (nh, nkv, theta, window, e1, e2) in enumerate([(2, 1, 700.0, None, 1e-5, 1e-4), (4, 2, 9000.0, 11, 1e-6, 1e-5)]):
+            x = ln(x + attention(x, l, nh, nkv, theta, window), f"l{l}.norm1", e1)
+            mw = {f"{n}_proj.weight": tensors[f"l{l}.feed_forward.{n}.weight"] for n in ("gate", "up", "down")}
+            x = ln(x + plain.swiglu_mlp(x, mw, ""), f"l{l}.norm2", e2)
+        return ln(x, "fn", 1e-5) @ tensors["emb"].T
+
+    ids = {"p": helpers.random_ids(33, V, 4), "q": helpers.random_ids(14, V, 5), "r": helpers.random_ids(21, V, 6)}
+    ref = {rid: reference(t) for rid, t in ids.items()}
+    for options in (dict(use_cuda_graph=False), dict(use_cuda_graph=True, graph_batch_sizes=(1, 2, 4), graph_prefill_tokens=7)):
+        runner = _runner(model, dtype=dtype, **options)
+        for steps in (helpers.trace_whole(ids), helpers.trace_tail_decode(ids, 6),
+                      helpers.trace_mixed(ids, max_live=3, seed=8, chunk_sizes=(7, 2, 7, 3))):
+            want = helpers.expected_logits(steps, ids, ref)
+            for i, (g, w) in enumerate(zip(helpers.replay(runner, steps), want)):
+                if w is not None:
+                    helpers.assert_close_logits(g, w, tolerance, f"post-norm step {i}")
+        assert all(gr.pool.in_use == 0 for gr in runner.cache.groups)
+    # the bias matters: without it the same model gives other logits
+    tensors["l0.norm1.bias"] = torch.zeros_like(tensors["l0.norm1.bias"])
+    assert float((reference(ids["p"]) - ref["p"]).abs().max()) > 1e-3
