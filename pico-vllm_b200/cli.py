@@ -92,7 +92,12 @@ def main(argv=None) -> int:
     rnd.add_argument("--std", type=float, default=0.02)
     rnd.set_defaults(fn=_random_model)
     args = ap.parse_args(argv)
-    return args.fn(args)
+    from .errors import PicoError
+    try:
+        return args.fn(args)
+    except PicoError as e:          # what the engine refuses on purpose: one line, no traceback
+        print(f"{type(e).__name__}: {e}", file=sys.stderr)
+        return 1
 
 
 if __name__ == "__main__":

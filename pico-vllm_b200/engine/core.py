@@ -12,7 +12,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..config.base import read_config_json
 from ..config.engine import EngineConfig
-from ..errors import ConfigError, OutOfPages
+from ..errors import ConfigError, KernelError, OutOfPages
 from ..registry import build_model, config_from_dict
 from ..weights.loader import load_weights, load_state_dict
 from .runner import ModelRunner
@@ -27,8 +27,15 @@ def _prepare_precision(dtype: str) -> None:
     torch.set_float32_matmul_precision("highest")
 
 
+def _require_device(device) -> None:
+    """Says in the engine's own words that there is no GPU, before torch says it in its own."""
+    if torch.device(device).type == "cuda" and not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this engine runs on a GPU only (there is no CPU path)")
+
+
 def load_model(model_dir: str, cfg: EngineConfig):
     """Model of the folder's architecture with its weights on the device."""
+    _require_device(cfg.device)
     config = config_from_dict(read_config_json(model_dir), where=f"{model_dir}/config.json")
     model = build_model(config)
     _prepare_precision(cfg.dtype)
@@ -40,6 +47,7 @@ def load_model(model_dir: str, cfg: EngineConfig):
 
 def model_from_tensors(config, tensors, cfg: EngineConfig):
     """Same from a configuration object and tensors in memory (name -> tensor)."""
+    _require_device(cfg.device)
     model = build_model(config)
     _prepare_precision(cfg.dtype)
     dtype = TORCH_DTYPES[cfg.dtype]
